@@ -14,7 +14,7 @@ with a ``StateSpec``.  A slot's state rows are zeroed before the first step
 that uses the slot.
 
 Pool layout of one layer: ``[pages, 2 (key, value), kv heads, page size, head
-dim]``; the reference keeps K and V as two ``[layers, blocks, heads, 64, dim]``
+dim]`` (one plane instead of two where the spec says that a token's row serves as both); the reference keeps K and V as two ``[layers, blocks, heads, 64, dim]``
 tensors (rosellm/roseinfer/engine.py:4397-4408).
 
 All bookkeeping is on the host; device tensors are touched only by
@@ -100,7 +100,7 @@ class CacheManager:
             if allocate_pools:
                 for layer in layers:
                     group.pools[layer] = torch.zeros(
-                        (self.num_pages, 2, spec.num_kv_heads, self.page_size, spec.head_dim),
+                        (self.num_pages, spec.planes, spec.num_kv_heads, self.page_size, spec.head_dim),
                         dtype=dtype, device=self.device,
                     )
                 group.device_table = torch.full(

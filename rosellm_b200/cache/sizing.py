@@ -32,7 +32,7 @@ def kv_bytes_per_token(kv_specs, dtype: str) -> int:
     """Bytes of keys and values that one cached token takes over all layers
     (``kv_specs``: the ``KVCacheSpec`` of every layer that writes a cache)."""
     specs = kv_specs.values() if hasattr(kv_specs, "values") else kv_specs
-    return sum(2 * s.num_kv_heads * s.head_dim * ELEMENT_BYTES[dtype] for s in specs)
+    return sum(getattr(s, "planes", 2) * s.num_kv_heads * s.head_dim * ELEMENT_BYTES[dtype] for s in specs)
 
 
 def tokens_from_total_utilization(free_bytes: int, total_bytes: int, gpu_memory_utilization: float,

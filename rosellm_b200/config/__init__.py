@@ -12,12 +12,14 @@ from .base import (
 )
 from .engine import EngineConfig
 from .gpt2 import GPT2Config
+from .lebedra import LebedraConfig
 
 __all__ = [
     "Architecture",
     "ConfigError",
     "EngineConfig",
     "GPT2Config",
+    "LebedraConfig",
     "ModelConfig",
     "load_config",
     "parse_config",

@@ -1,7 +1,7 @@
 """Typed model configurations and the registry from architecture name to model.
 
-A model folder holds ``config.json``; its ``architectures[0]`` (or, failing
-that, ``model_type``) names the architecture.  The registry maps that name to
+A model folder holds ``config.json``; its ``architectures[0]`` (or a single
+``architecture``; failing both, ``model_type``) names the architecture.  The registry maps that name to
 a configuration class, which parses the architecture's own ``config.json``
 keys, and to a builder, which turns a parsed configuration into a
 ``ModelSpec`` (see ``rosellm_b200.parts.spec``).  Nothing else in the package
@@ -81,7 +81,7 @@ def registered_architectures() -> list[str]:
 
 
 def resolve_architecture(raw: dict[str, Any]) -> Architecture:
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []  # some folders name just one
     if isinstance(names, str):
         names = [names]
     for name in names:

@@ -1,0 +1,532 @@
+// Attention over a cache of latents: one row per token, shared by all heads, that serves as
+// key and as value.
+//
+// A mixer of this kind projects a token to a short latent c (normalised) and a rotated key
+// part k_r that all heads share, and caches only the row [c, k_r].  Per head the key would be
+// [W_uk c, k_r] and the value W_uv c; because both are linear in c, the query takes W_uk over
+// to its side (q_c = W_uk^T q_plain, computed by the per-head product in head_linear.cu) and
+// the value's W_uv is applied after the weighted sum.  What is left is attention of H query
+// rows [q_c, q_r] per token against the same cached rows, with the first `rank` entries of a
+// row as its value:
+//   s_j = scale * (q_c . c_j + q_r . k_r,j),  p = softmax over j <= position (with a sink),
+//   o = sum_j p_j c_j.
+// The sink is one more term exp(sink_h) in the denominator with no key and no value: the online
+// softmax starts from m = sink_h, l = 1, o = 0 instead of m = -inf, l = 0.  Scores, softmax and
+// sums are float32 in both precisions.
+//
+// Pool layout of one layer: [pages][page size][row width], row width = rank + rotated
+// entries, filled with zeros up to a multiple of 8 elements (rows start on 16-byte boundaries).
+//
+// Kernels: `latent_kv_write_kernel` (RMS norm of c, rotation of k_r, write into the page);
+// `latent_q_rope_kernel` (rotation of the queries' rotated part into the query rows);
+// `latent_attn_tile_kernel` (16 queries of one request and head against tiles of 32 keys in
+// shared memory: prompt portions, and decoded tokens in the 32-bit mode);
+// `latent_attn_decode_kernel` (a decoded token: one block takes all heads of a request and a
+// share of its keys, so that a cached row is read once for all heads) with
+// `latent_attn_merge_kernel`.
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "gemm_vec.cuh"
+
+namespace rl {
+
+// (u, v) at angle a -> (u cos a - v sin a, v cos a + u sin a); element j of the pair (2i, 2i+1).
+__device__ __forceinline__ float rotate_element(float u, float v, float angle, int odd) {
+  float s, c;
+  sincosf(angle, &s, &c);
+  return odd ? fmaf(v, c, u * s) : fmaf(u, c, -(v * s));
+}
+
+template <typename T>
+__global__ __launch_bounds__(128) void latent_kv_write_kernel(
+    const float* __restrict__ dkv, long ld, const float* __restrict__ gamma, float eps,
+    const float* __restrict__ inv_freq, int rot_dims, T* __restrict__ pool, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ positions, const int* __restrict__ req_of_token,
+    const int* __restrict__ slots, int n_tokens, int rank, int rot_dim, int row_width, int page_size, int max_pos,
+    int* __restrict__ status) {
+  __shared__ float scratch[33];
+  pdl_begin();
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  const int pos = positions[n];
+  const int slot = slots[req_of_token[n]];
+  if (slot < 0) return;  // padding of a fixed-size batch
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_POSITION);
+    return;
+  }
+  const int page = block_table[(size_t)slot * bt_stride + pos / page_size];
+  if (page < 0) {
+    if (threadIdx.x == 0) atomicOr(status, RL_STATUS_BAD_PAGE);
+    return;
+  }
+  const float* src = dkv + (size_t)n * ld;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) s = fmaf(src[d], src[d], s);
+  const float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)rank + eps);
+  T* dst = pool + ((size_t)page * page_size + pos % page_size) * row_width;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) dst[d] = from_f32<T>(src[d] * r * gamma[d]);
+  const float* kr = src + rank;
+  for (int j = threadIdx.x; j < row_width - rank; j += blockDim.x) {
+    float v = 0.f;
+    if (j < rot_dims) {
+      const int i = j >> 1;
+      v = rotate_element(kr[2 * i], kr[2 * i + 1], (float)pos * inv_freq[i], j & 1);
+    } else if (j < rot_dim) {
+      v = kr[j];
+    }
+    dst[rank + j] = from_f32<T>(v);
+  }
+}
+
+// The rotated part of every head's query, turned by the token's position, into the query rows
+// (entries [rank, row_width) of head h's row; beyond the rotated entries: zeros).
+template <typename T>
+__global__ __launch_bounds__(128) void latent_q_rope_kernel(
+    const T* __restrict__ q, long q_stride, int head_in, int plain, T* __restrict__ rows, long rows_stride,
+    int row_width, int rank, int rot_dim, int rot_dims, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, int n_tokens, int n_heads) {
+  pdl_begin();
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  const float pos = (float)positions[n];
+  const int tail = row_width - rank;
+  for (int i = threadIdx.x; i < n_heads * tail; i += blockDim.x) {
+    const int h = i / tail, j = i - h * tail;
+    const T* qr = q + (size_t)n * q_stride + (size_t)h * head_in + plain;
+    float v = 0.f;
+    if (j < rot_dims) {
+      const int pair = j >> 1;
+      v = rotate_element(to_f32(qr[2 * pair]), to_f32(qr[2 * pair + 1]), pos * inv_freq[pair], j & 1);
+    } else if (j < rot_dim) {
+      v = to_f32(qr[j]);
+    }
+    rows[(size_t)n * rows_stride + (size_t)h * row_width + rank + j] = from_f32<T>(v);
+  }
+}
+
+struct LatentParams {
+  const void* q;      // query row of token n, head h: q + n*q_stride + h*row_width
+  long q_stride;      // in elements
+  const void* pool;
+  const int* block_table;
+  int bt_stride;
+  const int* q_start;  // [requests+1]
+  const int* kv_len;   // [requests] rows the request has after this step's write
+  const int* slots;    // [requests]
+  void* out;           // out + n*out_stride + h*rank
+  long out_stride;
+  const float* sink;   // [heads], or null
+  int n_heads, rank, row_width, page_size;
+  float scale;
+  int* status;
+};
+
+constexpr int LT_Q = 16;     // queries per block
+constexpr int LT_KV = 32;    // keys per tile: one per lane
+constexpr int LT_ROWS = 4;   // queries per warp
+
+// Blocks [0, n_tiles): (request, first query) from `tiles`; blocks beyond: decoded requests.
+template <typename T, int NCHUNK>
+__global__ __launch_bounds__(128) void latent_attn_tile_kernel(LatentParams p, const int* __restrict__ tiles,
+                                                               int n_tiles, const int* __restrict__ decode_reqs) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_begin();
+  const int W = p.row_width;
+  float* q_s = smem;               // [LT_Q][W], scaled
+  float* k_s = q_s + LT_Q * W;     // [LT_KV][W+1]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int req, t0;
+  if ((int)blockIdx.x < n_tiles) {
+    req = tiles[2 * blockIdx.x];
+    t0 = tiles[2 * blockIdx.x + 1];
+  } else {
+    req = decode_reqs[blockIdx.x - n_tiles];
+    t0 = 0;
+  }
+  const int h = blockIdx.y;
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int rows = min(LT_Q, q_len - t0);
+  T* out = (T*)p.out;
+  const int slot = p.slots[req];
+  if (slot < 0) {  // padding of a fixed-size batch: no cache behind it
+    for (int i = tid; i < rows * p.rank; i += blockDim.x)
+      out[(size_t)(qs + t0 + i / p.rank) * p.out_stride + (size_t)h * p.rank + i % p.rank] = from_f32<T>(0.f);
+    return;
+  }
+  const int kv_len = p.kv_len[req];
+  const int pos0 = kv_len - q_len;
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+  const T* q = (const T*)p.q;
+  for (int i = tid; i < LT_Q * W; i += blockDim.x) {
+    const int r = i / W, d = i - r * W;
+    q_s[i] = r < rows ? to_f32(q[(size_t)(qs + t0 + r) * p.q_stride + (size_t)h * W + d]) * p.scale : 0.f;
+  }
+  const int first_pos = pos0 + t0;
+  const int kv_hi = first_pos + rows;
+  const float sink = p.sink != nullptr ? p.sink[h] : -CUDART_INF_F;
+  float m[LT_ROWS], l[LT_ROWS], o[LT_ROWS][NCHUNK];
+#pragma unroll
+  for (int r = 0; r < LT_ROWS; ++r) {
+    m[r] = sink;
+    l[r] = p.sink != nullptr ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) o[r][c] = 0.f;
+  }
+  const int W4 = W >> 2;
+  for (int kt = 0; kt < kv_hi; kt += LT_KV) {
+    __syncthreads();
+    for (int i = tid; i < LT_KV * W4; i += blockDim.x) {
+      const int j = i / W4, d = (i - j * W4) * 4;
+      const int key = kt + j;
+      float kk[4] = {0.f, 0.f, 0.f, 0.f};
+      if (key < kv_hi) {
+        const int page = bt[key / p.page_size];
+        if (page < 0)
+          atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        else
+          load4((const T*)p.pool + ((size_t)page * p.page_size + key % p.page_size) * W + d, kk);
+      }
+      float* kd = k_s + j * (W + 1) + d;
+      kd[0] = kk[0]; kd[1] = kk[1]; kd[2] = kk[2]; kd[3] = kk[3];
+    }
+    __syncthreads();
+    float s[LT_ROWS];
+#pragma unroll
+    for (int r = 0; r < LT_ROWS; ++r) s[r] = 0.f;
+    const float* kr = k_s + lane * (W + 1);
+    const float* qr = q_s + warp * LT_ROWS * W;
+    for (int d = 0; d < W; ++d) {
+      const float kd = kr[d];
+#pragma unroll
+      for (int r = 0; r < LT_ROWS; ++r) s[r] = fmaf(qr[r * W + d], kd, s[r]);
+    }
+    const int key = kt + lane;
+    float pr[LT_ROWS];
+#pragma unroll
+    for (int r = 0; r < LT_ROWS; ++r) {
+      const int row = warp * LT_ROWS + r;
+      const bool valid = row < rows && key <= first_pos + row;
+      const float sv = valid ? s[r] : -CUDART_INF_F;
+      const float m_new = fmaxf(m[r], warp_max(sv));
+      const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m[r] - m_new);
+      pr[r] = valid ? expf(sv - m_new) : 0.f;
+      l[r] = l[r] * alpha + warp_sum(pr[r]);
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) o[r][c] *= alpha;
+      m[r] = m_new;
+    }
+    const int cnt = min(LT_KV, kv_hi - kt);
+    for (int j = 0; j < cnt; ++j) {
+      float pj[LT_ROWS];
+#pragma unroll
+      for (int r = 0; r < LT_ROWS; ++r) pj[r] = __shfl_sync(0xffffffffu, pr[r], j);
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) {
+        const int d = lane + 32 * c;
+        const float vv = d < p.rank ? k_s[j * (W + 1) + d] : 0.f;
+#pragma unroll
+        for (int r = 0; r < LT_ROWS; ++r) o[r][c] = fmaf(pj[r], vv, o[r][c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < LT_ROWS; ++r) {
+    const int row = warp * LT_ROWS + r;
+    if (row >= rows) continue;
+    const float inv = 1.0f / l[r];
+#pragma unroll
+    for (int c = 0; c < NCHUNK; ++c) {
+      const int d = lane + 32 * c;
+      if (d < p.rank) out[(size_t)(qs + t0 + row) * p.out_stride + (size_t)h * p.rank + d] = from_f32<T>(o[r][c] * inv);
+    }
+  }
+}
+
+// A decoded token: block (request, split) takes the keys [beg, end) of the request for ALL
+// heads.  A tile of LD_KV cached rows is staged in shared memory once; warp w then serves heads
+// w, w + warps, ...: lane = key for the scores, lane = value entry for the weighted sum.
+// The queries of all heads lie in shared memory (float32, scaled).  Partial results
+// (m, l, o[rank]) per (request, head, split) are merged by latent_attn_merge_kernel; with one
+// split the result goes straight to `out`.  The sink belongs to split 0.
+constexpr int LD_KV = 32;
+constexpr int LD_WARPS = 8;
+
+template <typename T, int NCHUNK>
+__global__ __launch_bounds__(32 * LD_WARPS) void latent_attn_decode_kernel(
+    LatentParams p, const int* __restrict__ decode_reqs, int n_splits, float* __restrict__ part_o,
+    float* __restrict__ part_ml) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_begin();
+  const int W = p.row_width, H = p.n_heads;
+  float* k_s = smem;                      // [LD_KV][W+1]
+  float* q_s = k_s + LD_KV * (W + 1);     // [H][W]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int req = decode_reqs[blockIdx.x], sp = blockIdx.y;
+  const int n = p.q_start[req];
+  const int slot = p.slots[req];
+  T* out = (T*)p.out;
+  if (slot < 0) {
+    if (sp == 0)
+      for (int i = tid; i < H * p.rank; i += blockDim.x) out[(size_t)n * p.out_stride + i] = from_f32<T>(0.f);
+    return;
+  }
+  const int kv_len = p.kv_len[req];
+  const int chunk = ((kv_len + n_splits - 1) / n_splits + LD_KV - 1) / LD_KV * LD_KV;
+  const int beg = sp * chunk, end = min(kv_len, beg + chunk);
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+  const T* q = (const T*)p.q + (size_t)n * p.q_stride;
+  for (int i = tid; i < H * W; i += blockDim.x) q_s[i] = to_f32(q[i]) * p.scale;
+  const int W4 = W >> 2;
+  // this warp's heads: at most HPW of them are kept in registers at once
+  constexpr int HPW = 4;
+  for (int base = 0; base < H; base += LD_WARPS * HPW) {  // the same count for every warp: barriers inside
+    const int h0 = base + warp;
+    float m[HPW], l[HPW], o[HPW][NCHUNK];
+#pragma unroll
+    for (int r = 0; r < HPW; ++r) {
+      const int h = h0 + r * LD_WARPS;
+      const bool sinked = p.sink != nullptr && sp == 0 && h < H;
+      m[r] = sinked ? p.sink[h] : -CUDART_INF_F;
+      l[r] = sinked ? 1.f : 0.f;
+#pragma unroll
+      for (int c = 0; c < NCHUNK; ++c) o[r][c] = 0.f;
+    }
+    for (int kt = beg; kt < end; kt += LD_KV) {
+      __syncthreads();
+      for (int i = tid; i < LD_KV * W4; i += blockDim.x) {
+        const int j = i / W4, d = (i - j * W4) * 4;
+        const int key = kt + j;
+        float kk[4] = {0.f, 0.f, 0.f, 0.f};
+        if (key < end) {
+          const int page = bt[key / p.page_size];
+          if (page < 0)
+            atomicOr(p.status, RL_STATUS_BAD_PAGE);
+          else
+            load4((const T*)p.pool + ((size_t)page * p.page_size + key % p.page_size) * W + d, kk);
+        }
+        float* kd = k_s + j * (W + 1) + d;
+        kd[0] = kk[0]; kd[1] = kk[1]; kd[2] = kk[2]; kd[3] = kk[3];
+      }
+      __syncthreads();
+      const float* kr = k_s + lane * (W + 1);
+      const bool valid = kt + lane < end;
+      const int cnt = min(LD_KV, end - kt);
+      float pr[HPW];
+#pragma unroll
+      for (int r = 0; r < HPW; ++r) {
+        const int h = h0 + r * LD_WARPS;
+        pr[r] = 0.f;
+        if (h >= H) continue;  // the same for the whole warp
+        const float* qr = q_s + (size_t)h * W;
+        float s = 0.f;
+        for (int d = 0; d < W; ++d) s = fmaf(qr[d], kr[d], s);
+        const float sv = valid ? s : -CUDART_INF_F;
+        const float m_new = fmaxf(m[r], warp_max(sv));
+        const float alpha = m_new == -CUDART_INF_F ? 1.f : expf(m[r] - m_new);
+        pr[r] = valid ? expf(sv - m_new) : 0.f;
+        l[r] = l[r] * alpha + warp_sum(pr[r]);
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) o[r][c] *= alpha;
+        m[r] = m_new;
+      }
+      for (int j = 0; j < cnt; ++j) {
+        float pj[HPW];
+#pragma unroll
+        for (int r = 0; r < HPW; ++r) pj[r] = __shfl_sync(0xffffffffu, pr[r], j);
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+          const int d = lane + 32 * c;
+          const float vv = d < p.rank ? k_s[j * (W + 1) + d] : 0.f;
+#pragma unroll
+          for (int r = 0; r < HPW; ++r) o[r][c] = fmaf(pj[r], vv, o[r][c]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < HPW; ++r) {
+      const int h = h0 + r * LD_WARPS;
+      if (h >= H) continue;
+      if (n_splits == 1) {
+        const float inv = 1.0f / l[r];
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+          const int d = lane + 32 * c;
+          if (d < p.rank) out[(size_t)n * p.out_stride + (size_t)h * p.rank + d] = from_f32<T>(o[r][c] * inv);
+        }
+      } else {
+        const size_t row = ((size_t)blockIdx.x * H + h) * n_splits + sp;
+        if (lane == 0) {
+          part_ml[2 * row] = m[r];
+          part_ml[2 * row + 1] = l[r];
+        }
+#pragma unroll
+        for (int c = 0; c < NCHUNK; ++c) {
+          const int d = lane + 32 * c;
+          if (d < p.rank) part_o[row * p.rank + d] = o[r][c];
+        }
+      }
+    }
+  }
+}
+
+// out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits, in their order.
+template <typename T>
+__global__ void latent_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         int n_splits, const int* __restrict__ decode_reqs,
+                                         const int* __restrict__ q_start, const int* __restrict__ slots,
+                                         T* __restrict__ out, long out_stride, int n_heads, int rank) {
+  pdl_begin();
+  const int di = blockIdx.x, h = blockIdx.y;
+  const int req = decode_reqs[di];
+  if (slots[req] < 0) return;  // written by the decode kernel
+  const size_t row0 = ((size_t)di * n_heads + h) * n_splits;
+  float top = -CUDART_INF_F;
+  for (int s = 0; s < n_splits; ++s) top = fmaxf(top, part_ml[2 * (row0 + s)]);
+  float den = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = part_ml[2 * (row0 + s)];
+    den += (ms == -CUDART_INF_F ? 0.f : expf(ms - top)) * part_ml[2 * (row0 + s) + 1];
+  }
+  const float inv = 1.0f / den;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = part_ml[2 * (row0 + s)];
+      if (ms != -CUDART_INF_F) acc = fmaf(expf(ms - top), part_o[(row0 + s) * rank + d], acc);
+    }
+    out[(size_t)q_start[req] * out_stride + (size_t)h * rank + d] = from_f32<T>(acc * inv);
+  }
+}
+
+template <typename T, int NCHUNK>
+static inline void launch_latent(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
+                                 int n_decode, int n_splits, bool decode_by_request, float* part_o, float* part_ml,
+                                 cudaStream_t stream) {
+  const int W = p.row_width;
+  const int tile_blocks = n_tiles + (decode_by_request ? 0 : n_decode);
+  if (tile_blocks > 0) {
+    const size_t smem = (size_t)(LT_Q * W + LT_KV * (W + 1)) * sizeof(float);
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(latent_attn_tile_kernel<T, NCHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(latent_attn_tile_kernel<T, NCHUNK>, dim3(tile_blocks, p.n_heads), 128, smem, stream, p, tiles, n_tiles,
+               decode_reqs);
+  }
+  if (decode_by_request && n_decode > 0) {
+    const size_t smem = (size_t)(LD_KV * (W + 1) + p.n_heads * W) * sizeof(float);
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(latent_attn_decode_kernel<T, NCHUNK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(latent_attn_decode_kernel<T, NCHUNK>, dim3(n_decode, n_splits), 32 * LD_WARPS, smem, stream, p,
+               decode_reqs, n_splits, part_o, part_ml);
+    if (n_splits > 1)
+      launch_pdl(latent_attn_merge_kernel<T>, dim3(n_decode, p.n_heads), 64, 0, stream, (const float*)part_o,
+                 (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride, p.n_heads,
+                 p.rank);
+  }
+}
+
+template <typename T>
+static inline int dispatch_latent(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
+                                  int n_decode, int n_splits, bool by_request, float* part_o, float* part_ml,
+                                  cudaStream_t stream) {
+  const int chunks = (p.rank + 31) / 32;
+  if (chunks <= 1) launch_latent<T, 1>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, by_request, part_o, part_ml, stream);
+  else if (chunks <= 2) launch_latent<T, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, by_request, part_o, part_ml, stream);
+  else if (chunks <= 4) launch_latent<T, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, by_request, part_o, part_ml, stream);
+  else if (chunks <= 8) launch_latent<T, 8>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, by_request, part_o, part_ml, stream);
+  else if (chunks <= 16) launch_latent<T, 16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, by_request, part_o, part_ml, stream);
+  else return -2;
+  return 0;
+}
+
+}  // namespace rl
+
+// How many bytes of shared memory the kernels above may ask for.
+static constexpr size_t LATENT_SMEM_LIMIT = 200 * 1024;
+
+// 1 if the sizes fit the kernels (value width up to 512, shared memory), else 0.
+RL_EXPORT int rl_latent_attention_fits(int n_heads, int rank, int row_width) {
+  if (rank <= 0 || rank > 512 || row_width < rank || row_width % 8 != 0 || n_heads <= 0) return 0;
+  const size_t tile = (size_t)(rl::LT_Q * row_width + rl::LT_KV * (row_width + 1)) * sizeof(float);
+  return tile <= LATENT_SMEM_LIMIT ? 1 : 0;
+}
+
+// 1 if the all-heads decode kernel fits these sizes (its queries lie in shared memory).
+RL_EXPORT int rl_latent_decode_fits(int n_heads, int rank, int row_width) {
+  if (!rl_latent_attention_fits(n_heads, rank, row_width)) return 0;
+  const size_t smem = (size_t)(rl::LD_KV * (row_width + 1) + (size_t)n_heads * row_width) * sizeof(float);
+  return smem <= LATENT_SMEM_LIMIT ? 1 : 0;
+}
+
+// dkv: float32 [tokens, >= rank + rot_dim] with row stride ld: the first `rank` entries are
+// normalised (gamma, eps), the next `rot_dim` rotated in their first `rot_dims` entries.
+RL_EXPORT int rl_latent_kv_write(int dtype, const float* dkv, long ld, const float* gamma, float eps,
+                                 const float* inv_freq, int rot_dims, void* pool, const int* block_table,
+                                 int bt_stride, const int* positions, const int* req_of_token, const int* slots,
+                                 int n_tokens, int rank, int rot_dim, int row_width, int page_size, int max_pos,
+                                 int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || row_width < rank + rot_dim ||
+      status == nullptr)
+    return -2;
+  if (dtype == RL_F32)
+    rl::launch_pdl(rl::latent_kv_write_kernel<float>, n_tokens, 128, 0, stream, dkv, ld, gamma, eps, inv_freq, rot_dims,
+                   (float*)pool, block_table, bt_stride, positions, req_of_token, slots, n_tokens, rank, rot_dim,
+                   row_width, page_size, max_pos, status);
+  else
+    rl::launch_pdl(rl::latent_kv_write_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, dkv, ld, gamma, eps, inv_freq,
+                   rot_dims, (__nv_bfloat16*)pool, block_table, bt_stride, positions, req_of_token, slots, n_tokens,
+                   rank, rot_dim, row_width, page_size, max_pos, status);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// q: [tokens, heads * head_in] (row stride q_stride), head h's rotated part at h*head_in + plain;
+// rows: [tokens, heads * row_width] (row stride rows_stride), written at [rank, row_width).
+RL_EXPORT int rl_latent_q_rope(int dtype, const void* q, long q_stride, int head_in, int plain, void* rows,
+                               long rows_stride, int row_width, int rank, int rot_dim, int rot_dims,
+                               const float* inv_freq, const int* positions, int n_tokens, int n_heads,
+                               cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (rot_dims > rot_dim || (rot_dims & 1) || row_width < rank + rot_dim || plain + rot_dim > head_in) return -2;
+  if (dtype == RL_F32)
+    rl::launch_pdl(rl::latent_q_rope_kernel<float>, n_tokens, 128, 0, stream, (const float*)q, q_stride, head_in, plain,
+                   (float*)rows, rows_stride, row_width, rank, rot_dim, rot_dims, inv_freq, positions, n_tokens, n_heads);
+  else
+    rl::launch_pdl(rl::latent_q_rope_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, (const __nv_bfloat16*)q, q_stride,
+                   head_in, plain, (__nv_bfloat16*)rows, rows_stride, row_width, rank, rot_dim, rot_dims, inv_freq,
+                   positions, n_tokens, n_heads);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// tiles: [n_tiles][2] = (request, first query) of 16-query tiles of prompt portions;
+// decode_reqs: requests with one query.  decode_by_request: decoded requests go to the kernel
+// that takes all heads of a request in one block, their keys cut into n_splits parts
+// (part_o: n_decode*heads*n_splits*rank floats, part_ml: n_decode*heads*n_splits*2); otherwise
+// they are tiles of one query.
+RL_EXPORT int rl_latent_attention(int dtype, const void* q, long q_stride, const void* pool, const int* block_table,
+                                  int bt_stride, const int* q_start, const int* kv_len, const int* slots, void* out,
+                                  long out_stride, const float* sink, int n_heads, int rank, int row_width,
+                                  int page_size, float scale, const int* tiles, int n_tiles, const int* decode_reqs,
+                                  int n_decode, int decode_by_request, int n_splits, float* part_o, float* part_ml,
+                                  int* status, cudaStream_t stream) {
+  if (!rl_latent_attention_fits(n_heads, rank, row_width) || status == nullptr) return -2;
+  if (decode_by_request && !rl_latent_decode_fits(n_heads, rank, row_width)) return -3;
+  if (n_splits < 1 || n_splits > 65535 || (decode_by_request && n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
+    return -4;
+  rl::LatentParams p{q, q_stride, pool, block_table, bt_stride, q_start, kv_len, slots, out, out_stride, sink,
+                     n_heads, rank, row_width, page_size, scale, status};
+  int rc;
+  if (dtype == RL_F32)
+    rc = rl::dispatch_latent<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_by_request != 0, part_o,
+                                    part_ml, stream);
+  else
+    rc = rl::dispatch_latent<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_by_request != 0,
+                                            part_o, part_ml, stream);
+  if (rc != 0) return rc;
+  RL_CHECK_LAUNCH();
+  return 0;
+}

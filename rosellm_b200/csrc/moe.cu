@@ -1,0 +1,325 @@
+// Mixture of experts: routing, and the experts' gated feed-forward as grouped products.
+//
+// Routing (`moe_select_kernel`, one warp per token, float32): scores s = softmax(z) over all
+// experts; the choice is made on s + correction, the weights are the chosen experts' s.  With
+// groups, the experts form `group_count` equal groups of neighbours, a group's score is the
+// largest choice score in it, and only experts of the best `group_keep` groups can be chosen
+// (the others count as minus infinity).  Ties go to the lower index.
+//
+// The chosen (token, expert) pairs are then laid out expert by expert (`moe_plan_kernel`:
+// offsets and a list of row tiles from the per-expert counts; `moe_scatter_kernel`: a place for
+// every pair), all on the device: the host never learns the counts, so a step's launches depend
+// on its token count alone.  `moe_ffn1_kernel` computes a tile of f(h W_gate^T, h W_up^T) with
+// the rows of h gathered by token, `moe_ffn2_kernel` the tile's product with W_down, and
+// `moe_combine_kernel` sums a token's expert outputs in the order of its choices, times their
+// weights (a fixed order: the result does not depend on where the pairs were placed).
+// Products: IEEE float32 multiply-adds on 64 x 64 tiles (tile_gemm.cuh) in both precisions.
+#include <math_constants.h>
+
+#include "gated_act.cuh"
+#include "tile_gemm.cuh"
+
+namespace rl {
+
+constexpr int MOE_TILE_ROWS = TG_M;
+constexpr float MOE_TAKEN = 1e38f;  // marks a group that has been picked
+
+// The lane's candidate (value, index) merged over the warp: the largest value, among equals the
+// lowest index.
+__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > v || (ov == v && oi < idx)) {
+      v = ov;
+      idx = oi;
+    }
+  }
+}
+
+__global__ __launch_bounds__(128) void moe_select_kernel(const float* __restrict__ z, long ldz,
+                                                         const float* __restrict__ correction, int n_tokens,
+                                                         int n_experts, int top, int group_count, int group_keep,
+                                                         int* __restrict__ ids, float* __restrict__ weights,
+                                                         int* __restrict__ counts) {
+  extern __shared__ float smem[];
+  pdl_begin();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  const int E = n_experts;
+  float* s_w = smem + (size_t)warp * 3 * E;  // scores
+  float* c_w = s_w + E;                      // choice scores
+  float* g_w = c_w + E;                      // group scores
+  const float* zr = z + (size_t)t * ldz;
+  float mx = -CUDART_INF_F;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float ex = expf(zr[e] - mx);
+    s_w[e] = ex;
+    sum += ex;
+  }
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    const float s = s_w[e] / sum;
+    s_w[e] = s;
+    c_w[e] = s + (correction != nullptr ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (group_count > 1 && group_keep < group_count) {
+    const int per = E / group_count;
+    for (int g = lane; g < group_count; g += 32) {
+      float best = -CUDART_INF_F;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c_w[e]);
+      g_w[g] = best;
+    }
+    __syncwarp();
+    for (int pick = 0; pick < group_keep; ++pick) {
+      float v = -CUDART_INF_F;
+      int idx = 0x7fffffff;
+      for (int g = lane; g < group_count; g += 32) {
+        const float gv = g_w[g];
+        if (gv < MOE_TAKEN && (gv > v || idx == 0x7fffffff)) {
+          v = gv;
+          idx = g;
+        }
+      }
+      warp_argmax(v, idx);
+      if (lane == 0 && idx != 0x7fffffff) g_w[idx] = MOE_TAKEN;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (g_w[e / per] < MOE_TAKEN) c_w[e] = -CUDART_INF_F;
+    __syncwarp();
+  }
+  for (int j = 0; j < top; ++j) {
+    float v = -CUDART_INF_F;
+    int idx = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float cv = c_w[e];
+      if (cv > v || (idx == 0x7fffffff && cv > -CUDART_INF_F)) {
+        v = cv;
+        idx = e;
+      }
+    }
+    warp_argmax(v, idx);
+    if (idx == 0x7fffffff) idx = 0;  // fewer allowed experts than `top`: refused by the host before
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = idx;
+      weights[(size_t)t * top + j] = s_w[idx];
+      atomicAdd(&counts[idx], 1);
+      c_w[idx] = -CUDART_INF_F;
+    }
+    __syncwarp();
+  }
+}
+
+// One block.  offsets[e]: first place of expert e; tiles[k] = (expert, first place, rows);
+// meta[0]: number of tiles.  Leaves counts and fill zero.
+__global__ __launch_bounds__(256) void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ fill,
+                                                       int* __restrict__ offsets, int* __restrict__ tiles,
+                                                       int* __restrict__ meta, int n_experts) {
+  extern __shared__ int plan_s[];  // [E+1] offsets, [E+1] first tile
+  pdl_begin();
+  int* off_s = plan_s;
+  int* tile_s = plan_s + n_experts + 1;
+  if (threadIdx.x == 0) {
+    int at = 0, tile = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      off_s[e] = at;
+      tile_s[e] = tile;
+      const int c = counts[e];
+      at += c;
+      tile += (c + MOE_TILE_ROWS - 1) / MOE_TILE_ROWS;
+    }
+    off_s[n_experts] = at;
+    tile_s[n_experts] = tile;
+    meta[0] = tile;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    const int c = off_s[e + 1] - off_s[e];
+    for (int k = 0; k * MOE_TILE_ROWS < c; ++k) {
+      int* tl = tiles + 3 * (size_t)(tile_s[e] + k);
+      tl[0] = e;
+      tl[1] = off_s[e] + k * MOE_TILE_ROWS;
+      tl[2] = min(MOE_TILE_ROWS, c - k * MOE_TILE_ROWS);
+    }
+    offsets[e] = off_s[e];
+    counts[e] = 0;
+    fill[e] = 0;
+  }
+  if (threadIdx.x == 0) offsets[n_experts] = off_s[n_experts];
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ offsets,
+                                   int* __restrict__ fill, int* __restrict__ row_token, int* __restrict__ place_of,
+                                   int n_pairs, int top) {
+  pdl_begin();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  const int e = ids[i];
+  const int place = offsets[e] + atomicAdd(&fill[e], 1);
+  row_token[place] = i / top;
+  place_of[i] = place;
+}
+
+// act[place, f] = f(h[token] . W_gate[e, f], h[token] . W_up[e, f]).  w_gu: [experts][2][ff][hidden].
+template <typename T>
+__global__ __launch_bounds__(256) void moe_ffn1_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ w_gu,
+                                                       const int* __restrict__ tiles, const int* __restrict__ meta,
+                                                       const int* __restrict__ row_token, T* __restrict__ act,
+                                                       long lda, int hidden, int ff, int kind, float alpha,
+                                                       float limit) {
+  __shared__ TileGemmSmem s;
+  __shared__ float up_s[TG_K][TG_N + 1];
+  __shared__ int tok[TG_M];
+  pdl_begin();
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * TG_N;
+  if (threadIdx.x < TG_M) tok[threadIdx.x] = threadIdx.x < rows ? row_token[row0 + threadIdx.x] : 0;
+  __syncthreads();
+  const T* wg = w_gu + (size_t)e * 2 * ff * hidden;
+  const T* wu = wg + (size_t)ff * hidden;
+  float acc_g[4][4] = {}, acc_u[4][4] = {};
+  tile_gemm_pair(
+      acc_g, acc_u, hidden,
+      [&](int m, int k) { return (m < rows && k < hidden) ? to_f32(h[(size_t)tok[m] * ldh + k]) : 0.f; },
+      [&](int k, int n) { return (n0 + n < ff && k < hidden) ? to_f32(wg[(size_t)(n0 + n) * hidden + k]) : 0.f; },
+      [&](int k, int n) { return (n0 + n < ff && k < hidden) ? to_f32(wu[(size_t)(n0 + n) * hidden + k]) : 0.f; },
+      s, up_s);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < ff) act[(size_t)(row0 + m) * lda + n] = from_f32<T>(gated_value(acc_g[i][j], acc_u[i][j], kind, alpha, limit));
+    }
+  }
+}
+
+// eo[place, :] = act[place, :] W_down[e]^T.  w_down: [experts][hidden][ff]; eo float32.
+template <typename T>
+__global__ __launch_bounds__(256) void moe_ffn2_kernel(const T* __restrict__ act, long lda,
+                                                       const T* __restrict__ w_down, const int* __restrict__ tiles,
+                                                       const int* __restrict__ meta, float* __restrict__ eo,
+                                                       int hidden, int ff) {
+  __shared__ TileGemmSmem s;
+  pdl_begin();
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * TG_N;
+  const T* wd = w_down + (size_t)e * hidden * ff;
+  float acc[4][4] = {};
+  tile_gemm(
+      acc, ff, [&](int m, int k) { return (m < rows && k < ff) ? to_f32(act[(size_t)(row0 + m) * lda + k]) : 0.f; },
+      [&](int k, int n) { return (n0 + n < hidden && k < ff) ? to_f32(wd[(size_t)(n0 + n) * ff + k]) : 0.f; }, s);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < hidden) eo[(size_t)(row0 + m) * hidden + n] = acc[i][j];
+    }
+  }
+}
+
+// y[t] (+)= sum_j weights[t, j] * eo[place_of[t, j]], j in order.
+__global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restrict__ eo,
+                                                          const float* __restrict__ weights,
+                                                          const int* __restrict__ place_of, float* __restrict__ y,
+                                                          long ldy, int n_tokens, int hidden, int top, int add) {
+  pdl_begin();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j)
+      acc = fmaf(weights[(size_t)t * top + j], eo[(size_t)place_of[(size_t)t * top + j] * hidden + d], acc);
+    float* o = y + (size_t)t * ldy + d;
+    *o = add ? *o + acc : acc;
+  }
+}
+
+}  // namespace rl
+
+// z: float32 router logits [tokens, experts] (row stride ldz).  ids, weights: [tokens * top].
+// counts: [experts], zero on entry; holds the experts' pair counts afterwards.
+RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, int n_tokens, int n_experts, int top,
+                            int group_count, int group_keep, int* ids, float* weights, int* counts,
+                            cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n_experts <= 0 || n_experts > 2048 || top <= 0 || top > n_experts) return -2;
+  if (group_count < 1 || n_experts % group_count != 0 || group_keep < 1 || group_keep > group_count ||
+      top > group_keep * (n_experts / group_count))
+    return -3;
+  const size_t smem = (size_t)4 * 3 * n_experts * sizeof(float);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(rl::moe_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  rl::launch_pdl(rl::moe_select_kernel, (n_tokens + 3) / 4, 128, smem, stream, z, ldz, correction, n_tokens, n_experts,
+                 top, group_count, group_keep, ids, weights, counts);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// The pairs laid out expert by expert: offsets [experts + 1], tiles [max_tiles][3], meta [1],
+// row_token and place_of [tokens * top].  counts as rl_moe_select left it; counts and fill are
+// zero afterwards.  max_tiles >= rl_moe_max_tiles(pairs, experts).
+RL_EXPORT int rl_moe_plan(const int* ids, int* counts, int* fill, int* offsets, int* tiles, int* meta, int* row_token,
+                          int* place_of, int n_tokens, int n_experts, int top, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (n_experts <= 0 || n_experts > 2048) return -2;
+  rl::launch_pdl(rl::moe_plan_kernel, 1, 256, (size_t)2 * (n_experts + 1) * sizeof(int), stream, counts, fill, offsets,
+                 tiles, meta, n_experts);
+  const int pairs = n_tokens * top;
+  rl::launch_pdl(rl::moe_scatter_kernel, (pairs + 255) / 256, 256, 0, stream, ids, (const int*)offsets, fill, row_token,
+                 place_of, pairs, top);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+RL_EXPORT int rl_moe_max_tiles(int n_pairs, int n_experts) {
+  return (n_pairs + rl::MOE_TILE_ROWS - 1) / rl::MOE_TILE_ROWS + n_experts;
+}
+
+// The experts' feed-forward on the laid-out pairs, and the weighted sum per token.
+// h: [tokens, hidden] (row stride ldh); w_gu: [experts][2][ff][hidden]; w_down:
+// [experts][hidden][ff]; act: scratch [pairs, ff] (row stride lda); eo: float32 scratch
+// [pairs, hidden]; y: float32 [tokens, hidden] (row stride ldy), overwritten or (add) added to.
+RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_gu, const void* w_down, const int* tiles,
+                             const int* meta, const int* row_token, const int* place_of, const float* weights,
+                             void* act, long lda, float* eo, float* y, long ldy, int n_tokens, int hidden, int ff,
+                             int n_experts, int top, int kind, float alpha, float limit, int add,
+                             cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hidden <= 0 || ff <= 0 || kind < 0 || kind > 3) return -2;
+  const int max_tiles = rl_moe_max_tiles(n_tokens * top, n_experts);
+  const dim3 g1(max_tiles, (ff + rl::TG_N - 1) / rl::TG_N), g2(max_tiles, (hidden + rl::TG_N - 1) / rl::TG_N);
+  if (g1.y > 65535 || g2.y > 65535) return -2;
+  if (dtype == RL_F32) {
+    rl::launch_pdl(rl::moe_ffn1_kernel<float>, g1, 256, 0, stream, (const float*)h, ldh, (const float*)w_gu, tiles,
+                   meta, row_token, (float*)act, lda, hidden, ff, kind, alpha, limit);
+    rl::launch_pdl(rl::moe_ffn2_kernel<float>, g2, 256, 0, stream, (const float*)act, lda, (const float*)w_down, tiles,
+                   meta, eo, hidden, ff);
+  } else {
+    rl::launch_pdl(rl::moe_ffn1_kernel<__nv_bfloat16>, g1, 256, 0, stream, (const __nv_bfloat16*)h, ldh,
+                   (const __nv_bfloat16*)w_gu, tiles, meta, row_token, (__nv_bfloat16*)act, lda, hidden, ff, kind,
+                   alpha, limit);
+    rl::launch_pdl(rl::moe_ffn2_kernel<__nv_bfloat16>, g2, 256, 0, stream, (const __nv_bfloat16*)act, lda,
+                   (const __nv_bfloat16*)w_down, tiles, meta, eo, hidden, ff);
+  }
+  rl::launch_pdl(rl::moe_combine_kernel, n_tokens, 256, 0, stream, (const float*)eo, weights, place_of, y, ldy,
+                 n_tokens, hidden, top, add);
+  RL_CHECK_LAUNCH();
+  return 0;
+}

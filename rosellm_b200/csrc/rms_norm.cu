@@ -1,0 +1,106 @@
+// RMS norm: y = x / sqrt(mean(x^2) + eps) * w, statistics and arithmetic in float32.
+//
+// Two uses.  `rmsnorm_store_kernel` writes normalised rows (optionally gathered by index) in
+// float32 or bfloat16: a final norm ahead of a head, or a norm ahead of a sublayer.
+// `rmsnorm_add_kernel` serves blocks that normalise a sublayer's OUTPUT: the float32 residual
+// stream gets `stream += mult * rmsnorm(y) * w`, and the same kernel may leave a bfloat16 copy
+// of the stream's new rows for the products of the next sublayer to read, so that no kernel of
+// its own has to round the stream.  `cast_rows_kernel` makes that copy where nothing precedes.
+#include "common.cuh"
+
+namespace rl {
+
+// One block per row; the row is read twice (the second time from L1/L2).
+template <typename TOut>
+__global__ __launch_bounds__(256) void rmsnorm_store_kernel(const float* __restrict__ x, long ldx,
+                                                            const int* __restrict__ rows,
+                                                            const float* __restrict__ gamma, TOut* __restrict__ out,
+                                                            long ldo, int n_out, int width, float eps) {
+  __shared__ float scratch[33];
+  pdl_begin();
+  const int i = blockIdx.x;
+  if (i >= n_out) return;
+  const int src = rows != nullptr ? rows[i] : i;
+  const float* xr = x + (size_t)src * ldx;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = xr[d];
+    s = fmaf(v, v, s);
+  }
+  const float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)width + eps);
+  TOut* o = out + (size_t)i * ldo;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = from_f32<TOut>(xr[d] * r * gamma[d]);
+}
+
+// stream[i] += mult * rmsnorm(y[i]) * gamma; copy[i] = bfloat16(stream[i]) when copy is given.
+__global__ __launch_bounds__(256) void rmsnorm_add_kernel(const float* __restrict__ y, long ldy,
+                                                          const float* __restrict__ gamma, float* __restrict__ stream,
+                                                          long lds, __nv_bfloat16* __restrict__ copy, long ldc,
+                                                          int n_rows, int width, float eps, float mult) {
+  __shared__ float scratch[33];
+  pdl_begin();
+  const int i = blockIdx.x;
+  if (i >= n_rows) return;
+  const float* yr = y + (size_t)i * ldy;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = yr[d];
+    s = fmaf(v, v, s);
+  }
+  const float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)width + eps);
+  float* xr = stream + (size_t)i * lds;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = xr[d] + mult * (yr[d] * r * gamma[d]);
+    xr[d] = v;
+    if (copy != nullptr) copy[(size_t)i * ldc + d] = __float2bfloat16_rn(v);
+  }
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long n) {
+  pdl_begin();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(x[i]);
+}
+
+static inline int norm_threads(int width) {
+  int t = (width + 3) / 4;
+  t = (t + 31) / 32 * 32;
+  return t < 32 ? 32 : (t > 256 ? 256 : t);
+}
+
+}  // namespace rl
+
+// out[i] = rmsnorm(x[rows[i]] or x[i]) * gamma.  out_dtype: RL_F32 or RL_BF16.
+RL_EXPORT int rl_rmsnorm(int out_dtype, const float* x, long ldx, const int* rows, const float* gamma, void* out,
+                         long ldo, int n_out, int width, float eps, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (width <= 0) return -2;
+  const int threads = rl::norm_threads(width);
+  if (out_dtype == RL_F32)
+    rl::launch_pdl(rl::rmsnorm_store_kernel<float>, n_out, threads, 0, stream, x, ldx, rows, gamma, (float*)out, ldo,
+                   n_out, width, eps);
+  else
+    rl::launch_pdl(rl::rmsnorm_store_kernel<__nv_bfloat16>, n_out, threads, 0, stream, x, ldx, rows, gamma,
+                   (__nv_bfloat16*)out, ldo, n_out, width, eps);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// stream += mult * rmsnorm(y) * gamma, with an optional bfloat16 copy of the stream's new rows.
+RL_EXPORT int rl_rmsnorm_add(const float* y, long ldy, const float* gamma, float* stream_rows, long lds, void* copy,
+                             long ldc, int n_rows, int width, float eps, float mult, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (width <= 0) return -2;
+  rl::launch_pdl(rl::rmsnorm_add_kernel, n_rows, rl::norm_threads(width), 0, stream, y, ldy, gamma, stream_rows, lds,
+                 (__nv_bfloat16*)copy, ldc, n_rows, width, eps, mult);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// out = bfloat16(x), n elements.
+RL_EXPORT int rl_cast_rows(const float* x, void* out, long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  rl::launch_pdl(rl::cast_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, (__nv_bfloat16*)out, n);
+  RL_CHECK_LAUNCH();
+  return 0;
+}

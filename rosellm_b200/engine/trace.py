@@ -68,6 +68,7 @@ def run(args: argparse.Namespace, lines, stats: dict | None = None) -> int:
             kv_cache_tokens=pool_tokens,
             max_num_seqs=args.max_requests,
             max_num_batched_tokens=max(pool_tokens, 64),
+            max_model_len=pool_tokens,  # no request can hold more than the pool does
             cuda_graphs=args.cuda_graphs,
             capture_graphs_at_start=False,
             device=args.device,

@@ -1,4 +1,5 @@
 from . import gpt2  # registers GPT2LMHeadModel
+from . import lebedra  # registers Lebedra
 from .model import Layer, Model, named_params_of_spec
 
-__all__ = ["Layer", "Model", "named_params_of_spec", "gpt2"]
+__all__ = ["Layer", "Model", "named_params_of_spec", "gpt2", "lebedra"]

@@ -174,12 +174,18 @@ class Model:
             self.named_params(), file_tensors, source=source,
             optional_prefixes=self.spec.optional_prefixes, ignored=self.spec.ignored_tensors,
         )
+        # a file tensor that several parts read (a table of which every layer takes a part) goes
+        # to the device once
+        placed: dict[tuple, torch.Tensor] = {}
+
+        def on_device(np_: NamedParam) -> torch.Tensor:
+            key = (np_.key, np_.spec.kind, np_.spec.transpose)
+            if key not in placed:
+                placed[key] = to_device_tensor(by_name[np_.key], np_.spec, self.dtype, self.device)
+            return placed[key]
+
         for part, ps in _parts_with_specs(self.spec, self):
-            bound = {
-                np_.spec.role: to_device_tensor(by_name[np_.key], np_.spec, self.dtype, self.device)
-                for np_ in _named(part, ps)
-            }
-            part.bind(bound)
+            part.bind({np_.spec.role: on_device(np_) for np_ in _named(part, ps)})
         if getattr(self.head, "tied", False):
             self.head.weight = self.embedding.weight
         self.loaded = True

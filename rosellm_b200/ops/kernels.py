@@ -93,7 +93,8 @@ class _RecordingLib:
 
 
 _QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster",
-            "rl_host_memory_on_device")  # library functions that launch nothing
+            "rl_host_memory_on_device", "rl_latent_attention_fits", "rl_latent_decode_fits",
+            "rl_moe_max_tiles")  # library functions that launch nothing
 
 
 class recording:
@@ -151,6 +152,25 @@ def _lib() -> ctypes.CDLL:
         lib.rl_attn_block_fused_cluster.argtypes = [I, I, I]
         lib.rl_attn_block_fused.argtypes = [P, L, P, P, F, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, P]
         lib.rl_mlp_fused.argtypes = [P, L, P, L, P, P, F, P, P, P, P, I, I, I, I, I, P, P]
+        lib.rl_rmsnorm.argtypes = [I, P, L, P, P, P, L, I, I, F, P]
+        lib.rl_rmsnorm_add.argtypes = [P, L, P, P, L, P, L, I, I, F, F, P]
+        lib.rl_cast_rows.argtypes = [P, P, L, P]
+        lib.rl_latent_attention_fits.argtypes = [I, I, I]
+        lib.rl_latent_decode_fits.argtypes = [I, I, I]
+        lib.rl_latent_kv_write.argtypes = [I, P, L, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
+        lib.rl_latent_q_rope.argtypes = [I, P, L, I, I, P, L, I, I, I, I, P, P, I, I, P]
+        lib.rl_latent_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, P, I, I, I, I, F, P, I, P, I, I, I, P, P, P, P]
+        lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P]
+        lib.rl_gated_act.argtypes = [I, P, L, I, P, L, I, I, I, F, F, P]
+        lib.rl_token_gate.argtypes = [I, P, L, P, P, L, I, I, P, L, I, I, I, P, I, P, P]
+        lib.rl_moe_select.argtypes = [P, L, P, I, I, I, I, I, P, P, P, P]
+        lib.rl_moe_plan.argtypes = [P, P, P, P, P, P, P, P, I, I, I, P]
+        lib.rl_moe_max_tiles.argtypes = [I, I]
+        lib.rl_moe_experts.argtypes = [I, P, L, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, F, F, I, P]
+        for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
+                     "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
+                     "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts"):
+            getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
                      "rl_gemm_rows_bf16", "rl_gemm_rows_bf16_sample", "rl_attention", "rl_kv_write", "rl_sample", "rl_mlp_fused_slice", "rl_mlp_fused",
@@ -903,3 +923,231 @@ def _sample_scratch(device: torch.device, rows: int) -> tuple[torch.Tensor, torc
                 torch.zeros(cap, dtype=torch.int32, device=device))
         _sample_bufs[key] = have
     return have
+
+
+# ---- RMS norm --------------------------------------------------------------------------------
+
+def rmsnorm(x, gamma, eps: float, out, rows=None) -> None:
+    """out[i] = x[rows[i]] (or x[i]) / sqrt(mean(x^2) + eps) * gamma; x float32 (rows may be a
+    view with a row stride), out float32 or bfloat16."""
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(gamma, "gamma", torch.float32)
+    _need(out, "out", contiguous=False)
+    n_out, width = out.shape
+    if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != width or gamma.numel() != width:
+        raise KernelError("rmsnorm: widths differ, or rows are not contiguous")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n_out:
+            raise KernelError("rmsnorm: rows shorter than out")
+    elif x.shape[0] < n_out:
+        raise KernelError("rmsnorm: x has fewer rows than out")
+    _ok(_lib().rl_rmsnorm(_code(out), _ptr(x), x.stride(0), _ptr(rows), _ptr(gamma), _ptr(out), out.stride(0), n_out,
+                          width, float(eps), _stream()), "rmsnorm")
+
+
+def rmsnorm_add(y, gamma, eps: float, stream_rows, mult: float, copy=None) -> None:
+    """stream_rows += mult * y / sqrt(mean(y^2) + eps) * gamma (all float32); ``copy`` (bfloat16,
+    same shape) receives the rounded new rows of the stream."""
+    _need(y, "y", torch.float32, contiguous=False)
+    _need(gamma, "gamma", torch.float32)
+    _need(stream_rows, "stream_rows", torch.float32, contiguous=False)
+    n, width = stream_rows.shape
+    if tuple(y.shape) != (n, width) or gamma.numel() != width or y.stride(1) != 1 or stream_rows.stride(1) != 1:
+        raise KernelError("rmsnorm_add: shapes differ")
+    if copy is not None:
+        _need(copy, "copy", torch.bfloat16, contiguous=False)
+        if tuple(copy.shape) != (n, width) or copy.stride(1) != 1:
+            raise KernelError("rmsnorm_add: the copy has another shape")
+    _ok(_lib().rl_rmsnorm_add(_ptr(y), y.stride(0), _ptr(gamma), _ptr(stream_rows), stream_rows.stride(0), _ptr(copy),
+                              0 if copy is None else copy.stride(0), n, width, float(eps), float(mult), _stream()),
+        "rmsnorm_add")
+
+
+def cast_rows(x, out) -> None:
+    """out = bfloat16(x), both contiguous and of one shape."""
+    _need(x, "x", torch.float32)
+    _need(out, "out", torch.bfloat16)
+    if x.numel() != out.numel():
+        raise KernelError("cast_rows: sizes differ")
+    _ok(_lib().rl_cast_rows(_ptr(x), _ptr(out), x.numel(), _stream()), "cast_rows")
+
+
+# ---- attention over a cache of latents -----------------------------------------------------------
+
+def latent_attention_fits(n_heads: int, rank: int, row_width: int) -> bool:
+    return bool(_lib().rl_latent_attention_fits(n_heads, rank, row_width))
+
+
+def latent_decode_fits(n_heads: int, rank: int, row_width: int) -> bool:
+    """Whether decoded requests can take the kernel that serves all heads of a request in one block."""
+    return bool(_lib().rl_latent_decode_fits(n_heads, rank, row_width))
+
+
+def latent_kv_write(dkv, gamma, eps: float, inv_freq, rot_dims: int, pool, block_table, positions, req_of_token, slots,
+                    *, rank: int, rot_dim: int, max_pos: int) -> None:
+    """The step's cache rows: ``dkv`` float32 [tokens, rank + rot_dim]; the first ``rank`` entries
+    RMS-normalised (``gamma``, ``eps``), the next ``rot_dim`` rotated by the token's position in
+    their first ``rot_dims`` entries (pairs (2i, 2i+1), angle position * inv_freq[i]); written to
+    ``pool`` [pages, 1, 1, page size, row width] in the pool's dtype, zeros beyond."""
+    _need(dkv, "dkv", torch.float32, contiguous=False)
+    _need(gamma, "gamma", torch.float32)
+    _need(pool, "pool")
+    _need(block_table, "block_table", torch.int32)
+    n_pages, planes, heads, page_size, row_width = pool.shape
+    if planes != 1 or heads != 1 or dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1 or gamma.numel() != rank:
+        raise KernelError("latent_kv_write: the pool holds one row a token; dkv holds the latent and the rotated part")
+    if rot_dims:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() < rot_dims // 2:
+            raise KernelError("latent_kv_write: a frequency for every rotated pair")
+    rc = _lib().rl_latent_kv_write(_code(pool), _ptr(dkv), dkv.stride(0), _ptr(gamma), float(eps), _ptr(inv_freq),
+                                   rot_dims, _ptr(pool), _ptr(block_table), block_table.stride(0), _ptr(positions),
+                                   _ptr(req_of_token), _ptr(slots), dkv.shape[0], rank, rot_dim, row_width, page_size,
+                                   max_pos, _ptr(status_word(pool.device)), _stream())
+    _ok(rc, "latent_kv_write")
+
+
+def latent_q_rope(q, rows, inv_freq, positions, *, n_heads: int, head_in: int, plain: int, rank: int, rot_dim: int,
+                  rot_dims: int, row_width: int) -> None:
+    """rows[t, h, rank:row_width] = the rotated part of head h's query (q[t, h*head_in + plain:
+    ... + rot_dim]) turned by positions[t], then zeros."""
+    _need(q, "q", contiguous=False)
+    _need(rows, "rows", q.dtype, contiguous=False)
+    n = q.shape[0]
+    if q.shape[1] != n_heads * head_in or rows.shape[1] != n_heads * row_width or q.stride(1) != 1 or rows.stride(1) != 1:
+        raise KernelError("latent_q_rope: widths do not fit the heads")
+    rc = _lib().rl_latent_q_rope(_code(q), _ptr(q), q.stride(0), head_in, plain, _ptr(rows), rows.stride(0), row_width,
+                                 rank, rot_dim, rot_dims, _ptr(inv_freq), _ptr(positions), n, n_heads, _stream())
+    _ok(rc, "latent_q_rope")
+
+
+def latent_attention(q, pool, block_table, q_start, kv_len, slots, out, *, sink, n_heads: int, rank: int, scale: float,
+                     tiles, n_tiles: int, decode_reqs, n_decode: int, decode_by_request: bool = False,
+                     n_splits: int = 1, part_o=None, part_ml=None) -> None:
+    """Causal attention of the step's query rows ``q`` [tokens, heads * row width] over the cached
+    latent rows (``pool`` [pages, 1, 1, page size, row width]); a row's first ``rank`` entries are
+    its value; ``out`` [tokens, heads * rank].  ``sink`` float32 [heads] or ``None``.
+    ``decode_by_request``: decoded requests take the kernel that serves all heads in one block
+    and cuts a request's keys into ``n_splits`` parts (scratch ``part_o``, ``part_ml``)."""
+    _need(q, "q", contiguous=False)
+    _need(pool, "pool", q.dtype)
+    _need(out, "out", q.dtype, contiguous=False)
+    _, planes, heads, page_size, row_width = pool.shape
+    if planes != 1 or heads != 1 or q.shape[1] != n_heads * row_width or out.shape[1] != n_heads * rank:
+        raise KernelError("latent_attention: shapes do not fit the pool")
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+        if sink.numel() != n_heads:
+            raise KernelError("latent_attention: a sink per head")
+    if decode_by_request and n_splits > 1:
+        need = n_decode * n_heads * n_splits
+        if part_o is None or part_ml is None or part_o.numel() < need * rank or part_ml.numel() < need * 2:
+            raise KernelError("latent_attention: scratch for the split partial results is too small")
+    rc = _lib().rl_latent_attention(_code(q), _ptr(q), q.stride(0), _ptr(pool), _ptr(block_table), block_table.stride(0),
+                                    _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0), _ptr(sink),
+                                    n_heads, rank, row_width, page_size, float(scale), _ptr(tiles), n_tiles,
+                                    _ptr(decode_reqs), n_decode, int(decode_by_request), n_splits, _ptr(part_o),
+                                    _ptr(part_ml), _ptr(status_word(q.device)), _stream())
+    if rc in (-2, -3):
+        raise KernelError(f"latent_attention: sizes not taken (heads {n_heads}, value width {rank}, row width {row_width})")
+    _ok(rc, "latent_attention")
+    global _launches
+    if decode_by_request and n_decode:
+        _launches += (1 if n_tiles else 0) + (1 if n_splits > 1 else 0)
+
+
+def head_linear(inp, w, out, *, n_tokens: int, n_heads: int, k: int, n: int, in_strides, w_strides, out_strides) -> None:
+    """out[t, h, :n] = inp[t, h, :k] @ W_h for every head: element (t, h, i) of ``inp`` at
+    ``t*in_strides[0] + h*in_strides[1] + i``, element (h, i, j) of ``w`` at ``h*w_strides[0] +
+    i*w_strides[1] + j*w_strides[2]``, element (t, h, j) of ``out`` at ``t*out_strides[0] +
+    h*out_strides[1] + j`` (strides in elements; the tensors give base addresses and dtype)."""
+    _need(inp, "inp", contiguous=False)
+    _need(w, "w", inp.dtype)
+    _need(out, "out", inp.dtype, contiguous=False)
+    rc = _lib().rl_head_linear(_code(inp), _ptr(inp), in_strides[0], in_strides[1], _ptr(w), w_strides[0], w_strides[1],
+                               w_strides[2], _ptr(out), out_strides[0], out_strides[1], n_tokens, n_heads, k, n,
+                               _stream())
+    _ok(rc, "head_linear")
+
+
+# ---- gated feed-forward, token-gated input, mixture of experts ---------------------------------
+
+GATES = {"relu": 0, "silu": 1, "gelu_tanh": 2, "clamped_swish": 3}
+
+
+def gated_act(gu, out, *, width: int, up_at: int, gate: int, alpha: float = 1.0, limit: float = 0.0) -> None:
+    """out[r, f] = f(gu[r, f], gu[r, up_at + f]) for f < width (see csrc/gated_act.cuh)."""
+    _need(gu, "gu", contiguous=False)
+    _need(out, "out", gu.dtype, contiguous=False)
+    if gu.shape[1] < up_at + width or out.shape[1] < width or out.shape[0] != gu.shape[0]:
+        raise KernelError("gated_act: shapes do not fit")
+    _ok(_lib().rl_gated_act(_code(gu), _ptr(gu), gu.stride(0), up_at, _ptr(out), out.stride(0), gu.shape[0], width,
+                            gate, float(alpha), float(limit), _stream()), "gated_act")
+
+
+def token_gate(s, token_ids, table, col0: int, dim: int, out, feedback=None) -> None:
+    """out[n, j] = gelu_tanh(s[n, j]) * table[token_ids[n], col0 + j] for j < dim, zero beyond."""
+    _need(s, "s", contiguous=False)
+    _need(table, "table", s.dtype)
+    _need(out, "out", s.dtype, contiguous=False)
+    _need(token_ids, "token_ids", torch.int32)
+    if s.shape[1] < dim or out.shape[0] != s.shape[0] or col0 + dim > table.shape[1]:
+        raise KernelError("token_gate: shapes do not fit")
+    rc = _lib().rl_token_gate(_code(s), _ptr(s), s.stride(0), _ptr(token_ids), _ptr(table), table.stride(0), col0, dim,
+                              _ptr(out), out.stride(0), out.shape[1], s.shape[0], table.shape[0], _ptr(feedback),
+                              0 if feedback is None else feedback.numel(), _ptr(status_word(s.device)), _stream())
+    _ok(rc, "token_gate")
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    return int(_lib().rl_moe_max_tiles(n_pairs, n_experts))
+
+
+def moe_select(z, correction, *, top: int, group_count: int, group_keep: int, ids, weights, counts) -> None:
+    """Routing of every row of the float32 router logits ``z`` [tokens, experts]: see csrc/moe.cu.
+    ``ids`` int32 and ``weights`` float32 [tokens * top]; ``counts`` int32 [experts], zero on entry."""
+    _need(z, "z", torch.float32, contiguous=False)
+    n, n_experts = z.shape
+    for t, name, dt in ((ids, "ids", torch.int32), (weights, "weights", torch.float32), (counts, "counts", torch.int32)):
+        _need(t, name, dt)
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+    rc = _lib().rl_moe_select(_ptr(z), z.stride(0), _ptr(correction), n, n_experts, top, group_count, group_keep,
+                              _ptr(ids), _ptr(weights), _ptr(counts), _stream())
+    if rc in (-2, -3):
+        raise KernelError(f"moe_select: {n_experts} experts, top {top}, {group_keep} of {group_count} groups not taken")
+    _ok(rc, "moe_select")
+
+
+def moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, *, n_tokens: int, n_experts: int, top: int) -> None:
+    """Lay the chosen pairs out expert by expert (all int32 device buffers; see csrc/moe.cu)."""
+    rc = _lib().rl_moe_plan(_ptr(ids), _ptr(counts), _ptr(fill), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(row_token),
+                            _ptr(place_of), n_tokens, n_experts, top, _stream())
+    _ok(rc, "moe_plan")
+    global _launches
+    _launches += 1
+
+
+def moe_experts(h, w_gate_up, w_down, tiles, meta, row_token, place_of, weights, act, eo, y, *, n_experts: int, top: int,
+                ff: int, gate: int, alpha: float, limit: float, add: bool) -> None:
+    """The experts' gated feed-forward on the laid-out pairs and the weighted sum per token into
+    ``y`` float32 [tokens, hidden] (``add``: added to it).  ``w_gate_up`` [experts * 2 * ff, hidden]
+    (per expert: gate rows, then up rows), ``w_down`` [experts * hidden, ff]."""
+    _need(h, "h", contiguous=False)
+    _need(w_gate_up, "w_gate_up", h.dtype)
+    _need(w_down, "w_down", h.dtype)
+    _need(act, "act", h.dtype, contiguous=False)
+    _need(eo, "eo", torch.float32)
+    _need(y, "y", torch.float32, contiguous=False)
+    n, hidden = h.shape
+    if tuple(w_gate_up.shape) != (n_experts * 2 * ff, hidden) or tuple(w_down.shape) != (n_experts * hidden, ff) \
+            or act.shape[0] < n * top or act.shape[1] < ff or eo.numel() < n * top * hidden or tuple(y.shape) != (n, hidden):
+        raise KernelError("moe_experts: shapes do not fit")
+    rc = _lib().rl_moe_experts(_code(h), _ptr(h), h.stride(0), _ptr(w_gate_up), _ptr(w_down), _ptr(tiles), _ptr(meta),
+                               _ptr(row_token), _ptr(place_of), _ptr(weights), _ptr(act), act.stride(0), _ptr(eo), _ptr(y),
+                               y.stride(0), n, hidden, ff, n_experts, top, gate, float(alpha), float(limit), int(add),
+                               _stream())
+    _ok(rc, "moe_experts")
+    global _launches
+    _launches += 2

@@ -14,10 +14,13 @@ Categories and the signature of ``forward``:
                    ``rotate(ctx, q, k)``: in-place encoding of queries and keys.
 ``norm``           ``forward(ctx, x, rows=None) -> h``: normalised rows of the
                    residual stream in the activation dtype.
-``mixer``          ``forward(ctx, run, h, x)``: mixes tokens of a request and
-                   adds the result to ``x`` in place.  ``run`` tells which
-                   layer's cache or state to use and whether to append to it.
-``feed_forward``   ``forward(ctx, h, x)``: adds its result to ``x`` in place.
+``mixer``          ``forward(ctx, run, h, x, add=True)``: mixes tokens of a request and
+                   adds the result to ``x`` in place (``add=False``: writes it
+                   there instead, for blocks that normalise a sublayer's output
+                   before it joins the stream).  ``run`` tells which layer's
+                   cache or state to use and whether to append to it.
+``feed_forward``   ``forward(ctx, h, x, add=True)``: adds its result to ``x`` in
+                   place, or with ``add=False`` writes it there.
 ``block``          ``forward(ctx, run, layer, x)``: arranges norms, mixer and
                    feed-forward of one layer around the residual stream.
 ``head``           ``forward(ctx, h) -> logits`` ``[rows, vocab]`` float32.
@@ -84,11 +87,14 @@ class ParamSpec:
 @dataclass(frozen=True)
 class KVCacheSpec:
     """Keys and values in pages.  ``window``: how many latest keys a query sees
-    (``None``: all of them); older pages are given back while the request lives."""
+    (``None``: all of them); older pages are given back while the request lives.
+    ``planes``: 2 for keys and values kept apart; 1 where one cached row per token serves as
+    both (a latent that the mixer's queries and outputs are projected onto)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)

@@ -52,6 +52,45 @@ class LearnedAbsolutePositions(Part):
         return None
 
 
+def rotary_frequencies(dims: int, base: float) -> torch.Tensor:
+    """f_i = base^(-2i/dims) for the pairs i = 0 .. dims/2 - 1, evaluated in float64 and kept
+    in float32 (the kernels form the angle position * f_i in float32)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims).to(torch.float32)
+
+
+@register_part("position", "rotary")
+class RotaryPositions(Part):
+    """Rotation of queries and keys by their positions: of every head's ``head_dim`` entries the
+    first ``dims`` are turned, entry 2i with entry 2i+1 (the interleaved layout) by the angle
+    position * base^(-2i/dims); the rest pass unchanged.  Angles and rotation in float32.
+
+    A mixer whose rotation has constants of its own builds one for itself (``RotaryPositions(
+    dims=..., base=...)``) and asks it for ``frequencies(device)``; as a model's ``position``
+    part it has no table for the embedding to add."""
+
+    graph_safe = True
+    launches_replayable = True
+    rotates = True
+
+    def __init__(self, dims: int, base: float) -> None:
+        if dims < 0 or dims % 2:
+            raise ValueError(f"rotary dims {dims}: pairs are turned, the count must be even")
+        if base <= 0:
+            raise ValueError(f"rotary base {base} must be positive")
+        self.dims, self.base = int(dims), float(base)
+        self._freq: dict = {}
+
+    def table(self):
+        return None
+
+    def frequencies(self, device) -> torch.Tensor:
+        key = str(device)
+        if key not in self._freq:
+            self._freq[key] = rotary_frequencies(max(self.dims, 2), self.base).to(device)
+        return self._freq[key]
+
+
 @register_part("embedding", "token_table")
 class TokenEmbedding(Part):
     graph_safe = True
@@ -103,6 +142,38 @@ class LayerNorm(Part):
         out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
         K.layernorm(x, self.weight, self.bias, self.eps, out, rows)
         return out
+
+
+@register_part("norm", "rms_norm")
+class RMSNorm(Part):
+    """``x / sqrt(mean(x^2) + eps) * weight`` over the last dimension, in float32.
+
+    ``forward`` normalises rows of the stream for a consumer (a head, a pre-norm block).
+    ``add_to`` serves blocks that normalise a sublayer's output instead of its input:
+    ``stream += mult * norm(y)``, leaving (bfloat16 mode) the rounded new rows in ``copy`` for the
+    next sublayer's products."""
+
+    graph_safe = True
+    launches_replayable = True
+
+    def __init__(self, hidden_size: int, eps: float) -> None:
+        if eps <= 0:
+            raise ValueError("the norm's eps must be positive")
+        self.hidden_size = hidden_size
+        self.eps = float(eps)
+        self.weight = None
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.hidden_size,), kind="vector", init="ones")]
+
+    def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
+        n = x.shape[0] if rows is None else int(n_rows)
+        out = ctx.workspace.get(name, (n, self.hidden_size), ctx.act_dtype)
+        K.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out
+
+    def add_to(self, ctx, y, x, mult: float, copy=None) -> None:
+        K.rmsnorm_add(y, self.weight, self.eps, x, mult, copy)
 
 
 _NARROW_PARTS: dict[tuple, int] = {}  # (request-head pairs, keys, bytes a key, blocks at once) -> parts, as computed before
@@ -266,8 +337,8 @@ class CausalSelfAttention(Part):
                 and isinstance(h, K.NormInput) and h.x is x and n == ctx.n_decode == ctx.n_reqs and run.writes_cache
                 and not getattr(ctx.position, "rotates", True))
 
-    def forward(self, ctx, run, h, x) -> None:
-        if self._fused_decode(ctx, run, h, x):
+    def forward(self, ctx, run, h, x, add: bool = True) -> None:
+        if add and self._fused_decode(ctx, run, h, x):
             K.attn_block_fused(x, h, self.qkv_weight, self.qkv_bias, self._out_weight_packed, self.out_bias,
                                ctx.kv_pool(run.cache_key), ctx.block_table(run.cache_key), ctx.positions, ctx.slots,
                                n_heads=self.num_heads, scale=self.scale, max_pos=ctx.cache.max_seq_len)
@@ -312,7 +383,7 @@ class CausalSelfAttention(Part):
                     # prompt portions: the tcgen05 kernel (where its sizes fit) wins once a block
                     # walks several tiles of keys; short contexts are faster on mma.sync
                     prefill_path=None if self._tc_prompt_attention(ctx) else "mma")
-        K.linear(o, self.out_weight, self.out_bias, x, residual=True)
+        K.linear(o, self.out_weight, self.out_bias, x, residual=add)
 
 
 @register_part("feed_forward", "dense_mlp")
@@ -367,16 +438,16 @@ class DenseMLP(Part):
             if self._fused_slice:
                 self._out_weight_packed = K.mlp_pack_out_weight(self.out_weight, self._fused_slice)
 
-    def forward(self, ctx, h, x) -> None:
+    def forward(self, ctx, h, x, add: bool = True) -> None:
         # few rows: both products in one kernel, the inner activations never leave the SM
-        width = self._fused_slice if ctx.n_tokens <= 16 and K.FUSED_ROWS else 0
+        width = self._fused_slice if add and ctx.n_tokens <= 16 and K.FUSED_ROWS else 0
         if width:
             K.mlp_fused(x, h, self.in_weight, self.in_bias, self._out_weight_packed, self.out_bias, act=self.activation,
                         slice_width=width)
             return
         u = ctx.workspace.get("mlp_inner", (ctx.n_tokens, self.inner_padded), ctx.act_dtype)
         K.linear(h, self.in_weight, self.in_bias, u, act=self.activation)
-        K.linear(u, self.out_weight, self.out_bias, x, residual=True)
+        K.linear(u, self.out_weight, self.out_bias, x, residual=add)
 
 
 @register_part("block", "pre_norm")
@@ -401,6 +472,51 @@ class PreNormBlock(Part):
         if getattr(norm, "can_defer", False) and getattr(consumer, "takes_norm_input", False):
             return norm.forward(ctx, x, defer=True)
         return norm.forward(ctx, x)
+
+
+@register_part("block", "normed_sublayers")
+class NormedSublayersBlock(Part):
+    """Sublayers that read the stream itself and are normalised on the way back:
+    ``x += mult * norm(sublayer(x))`` for the mixer, then (where the layer has them) for the
+    feed-forward and for a token-gated input, each with a norm of its own.
+
+    The sublayers' products read the stream in the activation dtype: the stream itself in the
+    32-bit mode; in bfloat16 a rounded copy that the norm's kernel refreshes whenever it has
+    added to the stream (``ctx.extras["stream_copy"]``; the first layer of a step makes it)."""
+
+    graph_safe = True
+    launches_replayable = True
+
+    def __init__(self, residual_mult: float = 1.0, feed_forward: bool = True, token_input: bool = False) -> None:
+        self.mult = float(residual_mult)
+        self.uses = {"mixer": "mixer", "norm_mixer": "norm"}
+        if feed_forward:
+            self.uses.update(feed_forward="feed_forward", norm_feed_forward="norm")
+        if token_input:
+            self.uses.update(token_input="feed_forward", norm_token_input="norm")
+        self.has_feed_forward, self.has_token_input = feed_forward, token_input
+
+    @staticmethod
+    def _stream_input(ctx, x):
+        if ctx.act_dtype == torch.float32:
+            return x, None
+        h = ctx.extras.get("stream_copy")
+        if h is None:
+            h = ctx.extras["stream_copy"] = ctx.workspace.get("stream_copy", tuple(x.shape), ctx.act_dtype)
+            K.cast_rows(x, h)
+        return h, h
+
+    def forward(self, ctx, run, layer, x) -> None:
+        h, copy = self._stream_input(ctx, x)
+        y = ctx.workspace.get("sublayer_out", tuple(x.shape), torch.float32)
+        layer.mixer.forward(ctx, run, h, y, add=False)
+        layer.norm_mixer.add_to(ctx, y, x, self.mult, copy)
+        if self.has_feed_forward:
+            layer.feed_forward.forward(ctx, h, y, add=False)
+            layer.norm_feed_forward.add_to(ctx, y, x, self.mult, copy)
+        if self.has_token_input:
+            layer.token_input.forward(ctx, h, y, add=False)
+            layer.norm_token_input.add_to(ctx, y, x, self.mult, copy)
 
 
 @register_part("head", "tied_to_embedding")
