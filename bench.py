@@ -54,6 +54,10 @@ def parse_args():
     p.add_argument("--logits-then-sample", action="store_true",
                    help="write logits and sample from them in a kernel of its own, also where the head's product "
                         "could choose the tokens (for comparisons)")
+    p.add_argument("--compare-lebedra", action="store_true",
+                   help="instead of the default workload: prefill and decode of the Lebedra design (latent attention, "
+                        "mixture of experts) beside GPT-2 of equal width, depth and vocabulary, at layer sizes of "
+                        "real models, random weights")
     p.add_argument("--workloads", default="all", choices=["all", "none", "355M", "1.5B"],
                    help="the other two workloads (355M continuous batching, 1.5B decode and prefill)")
     return p.parse_args()
@@ -141,24 +145,26 @@ def prefill_flops(cfg, layers, n_seqs, seq_len, rows):
 class Harness:
     """An engine of one model with the measurements the bench takes of it."""
 
-    def __init__(self, cfg: dict, dtype: str, max_batch: int, graphs: bool = True, seed: int = 0, **engine_options):
+    def __init__(self, cfg, dtype: str, max_batch: int, graphs: bool = True, seed: int = 0, **engine_options):
         import numpy as np
 
         from rosellm_b200.config import GPT2Config
         from rosellm_b200.engine.llm import InferenceEngine
 
         self.cfg = cfg
-        self.config = GPT2Config(**cfg)
+        # a dict of GPT-2's sizes, or any architecture's typed configuration
+        self.config = GPT2Config(**cfg) if isinstance(cfg, dict) else cfg
         self.dtype = dtype
         self.elem = 2 if dtype == "bfloat16" else 4
+        positions = getattr(self.config, "n_positions", None) or self.config.max_positions
         options = dict(max_num_batched_tokens=2048, prefill_chunk_size=1024,
-                       kv_cache_max_tokens=max_batch * self.config.n_positions)
+                       kv_cache_max_tokens=max_batch * positions)
         options.update(engine_options)
         self.eng = InferenceEngine(config=self.config, seed=seed, dtype=dtype, max_batch_size=max_batch,
                                    cuda_graphs=graphs, **options)
         self.runner = self.eng.runner
         self.rng = np.random.default_rng(0)
-        self.vocab = self.config.vocab_size
+        self.vocab = self.runner.spec.vocab_size
 
     def close(self):
         import gc
@@ -606,11 +612,72 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
 
 
+# Layer sizes for --compare-lebedra: (width, heads, plain/rotated/value size per head, latent,
+# dense inner size, experts, top, expert inner size, groups, kept, token-input size).
+LEBEDRA_SIZES = {
+    "1024": dict(width=1024, heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=256, ff=4096, experts=16, top=2,
+                 expert_ff=1024, groups=4, keep=2, side=64),
+    "2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, ff=8192, experts=32, top=4,
+                 expert_ff=1408, groups=8, keep=4, side=128),
+}
+
+
+def lebedra_config(z: dict, layers: int, vocab: int, positions: int):
+    """Layer 0 with the dense feed-forward, the others with experts."""
+    from rosellm_b200.config.lebedra import LebedraConfig
+
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": {"dims": z["rot_dim"], "base": 10000.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    return LebedraConfig.from_dict({
+        "architecture": "Lebedra", "vocab": vocab, "width": z["width"], "residual_mult": 0.5, "norm": {"eps": 1e-6},
+        "token_side": {"dim": z["side"]}, "max_positions": positions,
+        "layers": [{"type": "latent_attention", "mixer": mixer,
+                    "mlp": {"kind": "dense", "ff": z["ff"]} if i == 0 else moe} for i in range(layers)]})
+
+
+def compare_lebedra(args):
+    """Prefill (2 x 1024 tokens) and decode (batch 8 and 64, 512 cached tokens) of Lebedra and of
+    GPT-2 at equal width, depth and vocabulary: device time by CUDA events, as the default workload."""
+    layers, vocab, positions = 4, 32000, 1024
+    clocks = Clocks()
+    clocks.start()
+    out = {"metric": "prefill and decode of Lebedra beside GPT-2 at equal width", "unit": "tokens/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": args.warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+           "data": "synthetic (random token ids, random weights)", "layers": layers, "vocab": vocab, "sizes": {}}
+    for name, z in LEBEDRA_SIZES.items():
+        row = {}
+        gpt2 = dict(n_layer=layers, n_embd=z["width"], n_head=z["width"] // 64, n_inner=4 * z["width"],
+                    vocab_size=vocab, n_positions=positions, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+        for label, cfg in (("lebedra", lebedra_config(z, layers, vocab, positions)), ("gpt2", gpt2)):
+            h = Harness(cfg, args.dtype, 64, graphs=not args.no_graphs)
+            try:
+                pms = h.prefill()
+                rec = {"prefill_2x1024_ms": round(pms, 4), "prefill_tok_s": round(2048 / (pms * 1e-3), 1),
+                       "weight_mb": round(h.runner.model.weight_bytes() / 1e6, 1)}
+                for b in (8, 64):
+                    ms, launches, gms, _ = h.device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
+                    rec[f"decode_b{b}_ms"] = round(ms, 4)
+                    rec[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    if gms is not None:
+                        rec[f"decode_b{b}_graph_ms"] = round(gms, 4)
+                row[label] = rec
+            finally:
+                h.close()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         sys.exit(2)
+    if args.compare_lebedra:
+        return compare_lebedra(args)
     if args.impl == "reference":
         run_reference(args)
     else:

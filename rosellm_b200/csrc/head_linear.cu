@@ -5,8 +5,10 @@
 // of head h becomes q_plain W_uk,h (a [dim] row times a [dim, rank] matrix) and the head's
 // output (sum of probabilities x latents) W_uv,h^T (a [rank] row times [rank, vdim]).  Both
 // are this kernel; the weight of head h is reached by three strides (head, inner index, output
-// index), so either storage order is read as it lies in the file.  IEEE float32 multiply-adds
-// on 64 x 64 tiles (tile_gemm.cuh) in both precisions; inputs and outputs bfloat16 or float32.
+// index), so either storage order can be read.  float32: IEEE multiply-adds on 64 x 64 tiles
+// (tile_gemm.cuh).  bfloat16 with the weight's inner index contiguous: the tensor cores
+// (mma_tile.cuh), float32 accumulation; any other bfloat16 layout takes the float32 tiles.
+#include "mma_tile.cuh"
 #include "tile_gemm.cuh"
 
 namespace rl {
@@ -45,6 +47,29 @@ __global__ __launch_bounds__(256) void head_linear_kernel(const T* __restrict__ 
   }
 }
 
+// bfloat16 on the tensor cores; the weight's inner index is contiguous (w_k == 1).
+template <bool VEC>
+__global__ __launch_bounds__(128) void head_linear_mma_kernel(const __nv_bfloat16* __restrict__ in, long in_tok,
+                                                              long in_head, const __nv_bfloat16* __restrict__ w,
+                                                              long w_head, long w_n, __nv_bfloat16* __restrict__ out,
+                                                              long out_tok, long out_head, int n_tokens, int k_total,
+                                                              int n_total) {
+  __shared__ __align__(16) MmaTileSmem s;
+  pdl_begin();
+  const int h = blockIdx.z;
+  const int m0 = blockIdx.x * MT_M, n0 = blockIdx.y * MT_N;
+  const __nv_bfloat16* in_h = in + (size_t)h * in_head;
+  const __nv_bfloat16* w_h = w + (size_t)h * w_head;
+  float acc[2][4][4] = {};
+  mma_tile<VEC>(
+      acc, k_total, [&](int m) { return m0 + m < n_tokens ? in_h + (size_t)(m0 + m) * in_tok : nullptr; },
+      [&](int n) { return n0 + n < n_total ? w_h + (size_t)(n0 + n) * w_n : nullptr; }, s);
+  mma_for_each(acc, [&](int m, int n, int mi, int ni, int c) {
+    if (m0 + m < n_tokens && n0 + n < n_total)
+      out[(size_t)(m0 + m) * out_tok + (size_t)h * out_head + n0 + n] = __float2bfloat16_rn(acc[mi][ni][c]);
+  });
+}
+
 }  // namespace rl
 
 // in: element (t, h, k) at in + t*in_tok + h*in_head + k; w: element (h, k, n) at
@@ -59,7 +84,13 @@ RL_EXPORT int rl_head_linear(int dtype, const void* in, long in_tok, long in_hea
   if (dtype == RL_F32)
     rl::launch_pdl(rl::head_linear_kernel<float>, grid, 256, 0, stream, (const float*)in, in_tok, in_head,
                    (const float*)w, w_head, w_k, w_n, (float*)out, out_tok, out_head, n_tokens, k_total, n_total);
-  else
+  else if (w_k == 1) {
+    const bool vec = k_total % 8 == 0 && in_tok % 8 == 0 && in_head % 8 == 0 && w_head % 8 == 0 && w_n % 8 == 0 &&
+                     ((uintptr_t)in % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    auto kernel = vec ? rl::head_linear_mma_kernel<true> : rl::head_linear_mma_kernel<false>;
+    rl::launch_pdl(kernel, grid, 128, 0, stream, (const __nv_bfloat16*)in, in_tok, in_head, (const __nv_bfloat16*)w,
+                   w_head, w_n, (__nv_bfloat16*)out, out_tok, out_head, n_tokens, k_total, n_total);
+  } else
     rl::launch_pdl(rl::head_linear_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, in_tok,
                    in_head, (const __nv_bfloat16*)w, w_head, w_k, w_n, (__nv_bfloat16*)out, out_tok, out_head, n_tokens,
                    k_total, n_total);

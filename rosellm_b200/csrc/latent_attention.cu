@@ -17,7 +17,8 @@
 // Pool layout of one layer: [pages][page size][row width], row width = rank + rotated
 // entries, filled with zeros up to a multiple of 8 elements (rows start on 16-byte boundaries).
 //
-// Kernels: `latent_kv_write_kernel` (RMS norm of c, rotation of k_r, write into the page);
+// Kernels (the last three are the float32 path, and the bfloat16 path of sizes the tensor-core
+// kernel `latent_attn_mma_kernel` does not take): `latent_kv_write_kernel` (RMS norm of c, rotation of k_r, write into the page);
 // `latent_q_rope_kernel` (rotation of the queries' rotated part into the query rows);
 // `latent_attn_tile_kernel` (16 queries of one request and head against tiles of 32 keys in
 // shared memory: prompt portions, and decoded tokens in the 32-bit mode);
@@ -401,6 +402,269 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part_o, const
   }
 }
 
+// ---- bfloat16 on the tensor cores ---------------------------------------------------------------
+//
+// All heads of a token meet the same cached rows, so the (token, head) pairs of a request are
+// simply rows of one matrix Q': a block takes RB consecutive pairs (of up to 16 tokens of a
+// prompt portion, or the heads of one decoded token and one part of its keys) and walks the
+// keys in tiles of 32 staged in shared memory.  Per tile a warp computes S = Q' K^T for its 16
+// rows with mma.sync m16n8k16 (operands read straight from shared memory, whose row stride is
+// 4 words mod 8: no bank conflicts), masks by each row's own position, keeps the online softmax
+// of its rows in float32 (base 2; the sink is the starting value), repacks P from the
+// accumulator layout into A fragments and adds P V, V being the first `rank` columns of the
+// same tile, fetched transposed with ldmatrix.  A warp holds NVW value tiles of 8 columns;
+// latents beyond 256 entries are split over two warps that share their rows (DVS = 2).
+constexpr int LM_KT = 32;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ void mma_16x8x16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+template <int NVW, int DVS>
+__global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, const int* __restrict__ tiles,
+                                                              const int* __restrict__ decode_reqs, int decode,
+                                                              int n_splits, float* __restrict__ part_o,
+                                                              float* __restrict__ part_ml) {
+  using bf16 = __nv_bfloat16;
+  constexpr int RB = 16 * (4 / DVS);
+  extern __shared__ __align__(16) unsigned char latent_smem[];
+  pdl_begin();
+  const int W = p.row_width, H = p.n_heads;
+  const int Wk = (W + 15) & ~15, LD = Wk + 8, W8 = Wk >> 3;
+  bf16* q_s = reinterpret_cast<bf16*>(latent_smem);  // [RB][LD]
+  bf16* k_s = q_s + RB * LD;                         // [LM_KT][LD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  int req, t0 = 0, sp = 0;
+  if (!decode) {
+    req = tiles[2 * blockIdx.x];
+    t0 = tiles[2 * blockIdx.x + 1];
+  } else {
+    req = decode_reqs[blockIdx.x];
+    sp = blockIdx.z;
+  }
+  const int qs = p.q_start[req];
+  const int q_len = p.q_start[req + 1] - qs;
+  const int rows_total = (decode ? 1 : min(LT_Q, q_len - t0)) * H;
+  const int row0 = blockIdx.y * RB;
+  if (row0 >= rows_total) return;
+  bf16* out = (bf16*)p.out;
+  const int slot = p.slots[req];
+  if (slot < 0) {  // padding of a fixed-size batch
+    if (sp == 0)
+      for (int i = tid; i < min(RB, rows_total - row0) * p.rank; i += blockDim.x) {
+        const int gr = row0 + i / p.rank;
+        out[(size_t)(qs + t0 + gr / H) * p.out_stride + (size_t)(gr % H) * p.rank + i % p.rank] = __float2bfloat16_rn(0.f);
+      }
+    return;
+  }
+  const int kv_len = p.kv_len[req];
+  const int pos0 = kv_len - q_len;
+  const int* bt = p.block_table + (size_t)slot * p.bt_stride;
+  int beg = 0, end = pos0 + t0 + (min(rows_total, row0 + RB) - 1) / H + 1;
+  if (decode) {
+    const int chunk = ((kv_len + n_splits - 1) / n_splits + LM_KT - 1) / LM_KT * LM_KT;
+    beg = sp * chunk;
+    end = min(kv_len, beg + chunk);
+  }
+  const bf16* q = (const bf16*)p.q;
+  for (int i = tid; i < RB * W8; i += 128) {
+    const int r = i / W8, c = (i - r * W8) * 8;
+    const int gr = row0 + r;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (gr < rows_total && c < W)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(qs + t0 + gr / H) * p.q_stride + (size_t)(gr % H) * W + c);
+    *reinterpret_cast<uint4*>(q_s + r * LD + c) = v;
+  }
+  const int rg = warp / DVS, vh = warp % DVS;
+  const int row_a = row0 + rg * 16 + g, row_b = row_a + 8;
+  const int qpos_a = row_a < rows_total ? pos0 + t0 + row_a / H : -1;
+  const int qpos_b = row_b < rows_total ? pos0 + t0 + row_b / H : -1;
+  const float scale2 = p.scale * LOG2E;
+  const bool sinked = p.sink != nullptr && sp == 0;
+  float m_a = sinked && row_a < rows_total ? p.sink[row_a % H] * LOG2E : -CUDART_INF_F;
+  float m_b = sinked && row_b < rows_total ? p.sink[row_b % H] * LOG2E : -CUDART_INF_F;
+  float l_a = m_a == -CUDART_INF_F ? 0.f : 1.f, l_b = m_b == -CUDART_INF_F ? 0.f : 1.f;
+  float o[NVW][4];
+#pragma unroll
+  for (int i = 0; i < NVW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const bf16* qa = q_s + (rg * 16 + g) * LD + 2 * t;
+  const uint32_t k_s_addr = (uint32_t)__cvta_generic_to_shared(k_s);
+
+  for (int kt = beg; kt < end; kt += LM_KT) {
+    __syncthreads();  // the tile before has been used (first pass: q_s is written)
+    for (int i = tid; i < LM_KT * W8; i += 128) {
+      const int j = i / W8, c = (i - j * W8) * 8;
+      const int key = kt + j;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (key < end && c < W) {
+        const int page = bt[key / p.page_size];
+        if (page < 0)
+          atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        else
+          v = *reinterpret_cast<const uint4*>((const bf16*)p.pool + ((size_t)page * p.page_size + key % p.page_size) * W + c);
+      }
+      *reinterpret_cast<uint4*>(k_s + j * LD + c) = v;
+    }
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f;
+    for (int ks = 0; ks < Wk; ks += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(qa + ks);
+      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + ks);
+      a[2] = *reinterpret_cast<const uint32_t*>(qa + ks + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + ks + 8);
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) {
+        const bf16* kb = k_s + (ni * 8 + g) * LD + ks + 2 * t;
+        mma_16x8x16(s[ni], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+      }
+    }
+    // mask by each row's own position, online softmax in base 2
+    float top_a = -CUDART_INF_F, top_b = -CUDART_INF_F;
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = kt + ni * 8 + 2 * t + (c & 1);
+        const bool ok = key < end && key <= (c < 2 ? qpos_a : qpos_b);
+        s[ni][c] = ok ? s[ni][c] * scale2 : -CUDART_INF_F;
+        if (c < 2) top_a = fmaxf(top_a, s[ni][c]); else top_b = fmaxf(top_b, s[ni][c]);
+      }
+    const float new_a = fmaxf(m_a, quad_max(top_a)), new_b = fmaxf(m_b, quad_max(top_b));
+    const float alpha_a = new_a == -CUDART_INF_F ? 1.f : exp2f(m_a - new_a);
+    const float alpha_b = new_b == -CUDART_INF_F ? 1.f : exp2f(m_b - new_b);
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float top = c < 2 ? new_a : new_b;
+        const float pv = s[ni][c] == -CUDART_INF_F ? 0.f : exp2f(s[ni][c] - top);
+        s[ni][c] = pv;
+        if (c < 2) sum_a += pv; else sum_b += pv;
+      }
+    l_a = l_a * alpha_a + quad_sum(sum_a);
+    l_b = l_b * alpha_b + quad_sum(sum_b);
+    m_a = new_a;
+    m_b = new_b;
+#pragma unroll
+    for (int i = 0; i < NVW; ++i) {
+      o[i][0] *= alpha_a; o[i][1] *= alpha_a; o[i][2] *= alpha_b; o[i][3] *= alpha_b;
+    }
+    // P as A fragments of two steps of 16 keys, then O += P V with V read transposed
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+      pa[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+      pa[2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+      pa[3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+#pragma unroll
+      for (int nv = 0; nv < NVW; nv += 2) {
+        const int col = min((vh * NVW + nv + (lane >> 4)) * 8, Wk - 8);
+        const uint32_t addr = k_s_addr + (uint32_t)(((j * 16 + (lane & 15)) * LD + col) * 2);
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(addr));
+        mma_16x8x16(o[nv], pa, b0, b1);
+        mma_16x8x16(o[nv + 1], pa, b2, b3);
+      }
+    }
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int gr = half ? row_b : row_a;
+    if (gr >= rows_total) continue;
+    const float l = half ? l_b : l_a, m = half ? m_b : m_a;
+    const int tok = qs + t0 + gr / H, hd = gr % H;
+    if (!decode || n_splits == 1) {
+      const float inv = 1.0f / l;
+#pragma unroll
+      for (int nv = 0; nv < NVW; ++nv) {
+        const int d = (vh * NVW + nv) * 8 + 2 * t;
+        if (d < p.rank) out[(size_t)tok * p.out_stride + (size_t)hd * p.rank + d] = __float2bfloat16_rn(o[nv][2 * half] * inv);
+        if (d + 1 < p.rank)
+          out[(size_t)tok * p.out_stride + (size_t)hd * p.rank + d + 1] = __float2bfloat16_rn(o[nv][2 * half + 1] * inv);
+      }
+    } else {
+      const size_t prow = ((size_t)blockIdx.x * H + hd) * n_splits + sp;
+      if (t == 0 && vh == 0) {
+        part_ml[2 * prow] = m == -CUDART_INF_F ? m : m * LN2;  // the merge works in natural units
+        part_ml[2 * prow + 1] = l;
+      }
+#pragma unroll
+      for (int nv = 0; nv < NVW; ++nv) {
+        const int d = (vh * NVW + nv) * 8 + 2 * t;
+        if (d < p.rank) part_o[prow * p.rank + d] = o[nv][2 * half];
+        if (d + 1 < p.rank) part_o[prow * p.rank + d + 1] = o[nv][2 * half + 1];
+      }
+    }
+  }
+}
+
+template <int NVW, int DVS>
+static inline void launch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
+                                     int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  constexpr int RB = 16 * (4 / DVS);
+  const int Wk = (p.row_width + 15) & ~15;
+  const size_t smem = (size_t)(RB + LM_KT) * (Wk + 8) * 2;
+  static size_t granted = 0;
+  if (smem > 48 * 1024 && smem > granted) {
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NVW, DVS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    granted = smem;
+  }
+  if (n_tiles > 0)
+    launch_pdl(latent_attn_mma_kernel<NVW, DVS>, dim3(n_tiles, (LT_Q * p.n_heads + RB - 1) / RB), 128, smem, stream, p,
+               tiles, decode_reqs, 0, 1, part_o, part_ml);
+  if (n_decode > 0) {
+    launch_pdl(latent_attn_mma_kernel<NVW, DVS>, dim3(n_decode, (p.n_heads + RB - 1) / RB, n_splits), 128, smem, stream,
+               p, tiles, decode_reqs, 1, n_splits, part_o, part_ml);
+    if (n_splits > 1)
+      launch_pdl(latent_attn_merge_kernel<__nv_bfloat16>, dim3(n_decode, p.n_heads), 64, 0, stream,
+                 (const float*)part_o, (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots,
+                 (__nv_bfloat16*)p.out, p.out_stride, p.n_heads, p.rank);
+  }
+}
+
+// The tensor-core kernel for these sizes, or false when it does not take them.
+static inline bool dispatch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
+                                       int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  const int Wk = (p.row_width + 15) & ~15;
+  if ((size_t)(64 + LM_KT) * (Wk + 8) * 2 > 200 * 1024 || p.n_heads * LT_Q > 65535 * 16) return false;
+  const int n8 = (p.rank + 7) / 8;
+#define RL_LATENT_MMA(NVW, DVS) \
+  launch_latent_mma<NVW, DVS>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream)
+  if (n8 <= 2) RL_LATENT_MMA(2, 1);
+  else if (n8 <= 4) RL_LATENT_MMA(4, 1);
+  else if (n8 <= 8) RL_LATENT_MMA(8, 1);
+  else if (n8 <= 16) RL_LATENT_MMA(16, 1);
+  else if (n8 <= 32) RL_LATENT_MMA(32, 1);
+  else if (n8 <= 64) RL_LATENT_MMA(32, 2);
+  else return false;
+#undef RL_LATENT_MMA
+  return true;
+}
+
 template <typename T, int NCHUNK>
 static inline void launch_latent(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                  int n_decode, int n_splits, bool decode_by_request, float* part_o, float* part_ml,
@@ -506,24 +770,26 @@ RL_EXPORT int rl_latent_q_rope(int dtype, const void* q, long q_stride, int head
 // decode_reqs: requests with one query.  decode_by_request: decoded requests go to the kernel
 // that takes all heads of a request in one block, their keys cut into n_splits parts
 // (part_o: n_decode*heads*n_splits*rank floats, part_ml: n_decode*heads*n_splits*2); otherwise
-// they are tiles of one query.
+// they are tiles of one query.  bfloat16 runs on the tensor-core kernel (decoded requests then
+// always by request) unless simt_only is set (for comparisons) or its sizes do not fit.
 RL_EXPORT int rl_latent_attention(int dtype, const void* q, long q_stride, const void* pool, const int* block_table,
                                   int bt_stride, const int* q_start, const int* kv_len, const int* slots, void* out,
                                   long out_stride, const float* sink, int n_heads, int rank, int row_width,
                                   int page_size, float scale, const int* tiles, int n_tiles, const int* decode_reqs,
                                   int n_decode, int decode_by_request, int n_splits, float* part_o, float* part_ml,
-                                  int* status, cudaStream_t stream) {
+                                  int simt_only, int* status, cudaStream_t stream) {
   if (!rl_latent_attention_fits(n_heads, rank, row_width) || status == nullptr) return -2;
   if (decode_by_request && !rl_latent_decode_fits(n_heads, rank, row_width)) return -3;
   if (n_splits < 1 || n_splits > 65535 || (decode_by_request && n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
     return -4;
   rl::LatentParams p{q, q_stride, pool, block_table, bt_stride, q_start, kv_len, slots, out, out_stride, sink,
                      n_heads, rank, row_width, page_size, scale, status};
-  int rc;
+  int rc = 0;
   if (dtype == RL_F32)
     rc = rl::dispatch_latent<float>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_by_request != 0, part_o,
                                     part_ml, stream);
-  else
+  else if (!(simt_only == 0 && (n_decode == 0 || decode_by_request) &&
+             rl::dispatch_latent_mma(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream)))
     rc = rl::dispatch_latent<__nv_bfloat16>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, decode_by_request != 0,
                                             part_o, part_ml, stream);
   if (rc != 0) return rc;

@@ -1,0 +1,123 @@
+// A 64 x 64 output tile of a bfloat16 product on the tensor cores (mma.sync m16n8k16, float32
+// accumulation), for products whose operand rows are reached through index arithmetic of the
+// caller's (rows gathered by an index, one weight matrix per head or per expert).  Both
+// operands have their inner index contiguous: the caller gives row_a(m) and row_b(n), the
+// address of element 0 of row m of A and of row n of B (nullptr: a row of zeros).  128 threads;
+// warp w holds rows (w / 2) * 32 .. + 32 and columns (w % 2) * 32 .. + 32 as 2 x 4 pieces of
+// 16 x 8; lane (g = lane / 4, t = lane % 4) holds of piece (mi, ni) the elements
+// (g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1).
+// VEC: every row address is 16-byte aligned and the inner size a multiple of 8 (16-byte loads);
+// otherwise elements are fetched one by one.
+#pragma once
+#include "common.cuh"
+
+namespace rl {
+
+constexpr int MT_M = 64, MT_N = 64, MT_K = 32, MT_LD = MT_K + 8;
+
+struct MmaTileSmem {
+  __nv_bfloat16 a[MT_M][MT_LD];
+  __nv_bfloat16 b[MT_N][MT_LD];
+};
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// 64 rows x MT_K elements of an operand into shared memory, zeros beyond k_total and for null rows.
+template <bool VEC, class Row>
+__device__ __forceinline__ void mma_stage(__nv_bfloat16 (*dst)[MT_LD], Row row, int k0, int k_total) {
+  for (int i = threadIdx.x; i < 64 * (MT_K / 8); i += 128) {
+    const int m = i / (MT_K / 8), kv = (i % (MT_K / 8)) * 8;
+    const __nv_bfloat16* src = row(m);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src != nullptr && k0 + kv < k_total) {
+      if (VEC) {
+        v = *reinterpret_cast<const uint4*>(src + k0 + kv);
+      } else {
+        __nv_bfloat16 e[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] = k0 + kv + j < k_total ? src[k0 + kv + j] : __float2bfloat16_rn(0.f);
+        v = *reinterpret_cast<const uint4*>(e);
+      }
+    }
+    *reinterpret_cast<uint4*>(&dst[m][kv]) = v;
+  }
+}
+
+__device__ __forceinline__ void mma_step(float (&acc)[2][4][4], const __nv_bfloat16 (*a_s)[MT_LD],
+                                         const __nv_bfloat16 (*b_s)[MT_LD]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int m0 = (warp >> 1) * 32, n0 = (warp & 1) * 32;
+#pragma unroll
+  for (int kk = 0; kk < MT_K; kk += 16) {
+    uint32_t af[2][4], bf[4][2];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+      const int r = m0 + mi * 16 + g;
+      af[mi][0] = *reinterpret_cast<const uint32_t*>(&a_s[r][kk + 2 * t]);
+      af[mi][1] = *reinterpret_cast<const uint32_t*>(&a_s[r + 8][kk + 2 * t]);
+      af[mi][2] = *reinterpret_cast<const uint32_t*>(&a_s[r][kk + 2 * t + 8]);
+      af[mi][3] = *reinterpret_cast<const uint32_t*>(&a_s[r + 8][kk + 2 * t + 8]);
+    }
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      const int c = n0 + ni * 8 + g;
+      bf[ni][0] = *reinterpret_cast<const uint32_t*>(&b_s[c][kk + 2 * t]);
+      bf[ni][1] = *reinterpret_cast<const uint32_t*>(&b_s[c][kk + 2 * t + 8]);
+    }
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int ni = 0; ni < 4; ++ni) mma_bf16_16x8x16(acc[mi][ni], af[mi], bf[ni]);
+  }
+}
+
+template <bool VEC, class RowA, class RowB>
+__device__ __forceinline__ void mma_tile(float (&acc)[2][4][4], int k_total, RowA row_a, RowB row_b,
+                                         MmaTileSmem& s) {
+  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
+    mma_stage<VEC>(s.a, row_a, k0, k_total);
+    mma_stage<VEC>(s.b, row_b, k0, k_total);
+    __syncthreads();
+    mma_step(acc, s.a, s.b);
+    __syncthreads();
+  }
+}
+
+// Two weight operands that share A (a gate and an up projection of one input).
+template <bool VEC, class RowA, class RowB, class RowC>
+__device__ __forceinline__ void mma_tile_pair(float (&acc_b)[2][4][4], float (&acc_c)[2][4][4], int k_total,
+                                              RowA row_a, RowB row_b, RowC row_c, MmaTileSmem& s,
+                                              __nv_bfloat16 (*c_s)[MT_LD]) {
+  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
+    mma_stage<VEC>(s.a, row_a, k0, k_total);
+    mma_stage<VEC>(s.b, row_b, k0, k_total);
+    mma_stage<VEC>(c_s, row_c, k0, k_total);
+    __syncthreads();
+    mma_step(acc_b, s.a, s.b);
+    mma_step(acc_c, s.a, c_s);
+    __syncthreads();
+  }
+}
+
+// f(row, column, value) for every element of the tile this thread holds.
+template <class F>
+__device__ __forceinline__ void mma_for_each(const float (&acc)[2][4][4], F f) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int m0 = (warp >> 1) * 32, n0 = (warp & 1) * 32;
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        f(m0 + mi * 16 + g + (c >= 2 ? 8 : 0), n0 + ni * 8 + 2 * t + (c & 1), mi, ni, c);
+}
+
+}  // namespace rl

@@ -13,10 +13,12 @@
 // the rows of h gathered by token, `moe_ffn2_kernel` the tile's product with W_down, and
 // `moe_combine_kernel` sums a token's expert outputs in the order of its choices, times their
 // weights (a fixed order: the result does not depend on where the pairs were placed).
-// Products: IEEE float32 multiply-adds on 64 x 64 tiles (tile_gemm.cuh) in both precisions.
+// Products: float32 as IEEE multiply-adds on 64 x 64 tiles (tile_gemm.cuh); bfloat16 on the tensor
+// cores (mma_tile.cuh) with float32 accumulation.
 #include <math_constants.h>
 
 #include "gated_act.cuh"
+#include "mma_tile.cuh"
 #include "tile_gemm.cuh"
 
 namespace rl {
@@ -118,7 +120,8 @@ __global__ __launch_bounds__(128) void moe_select_kernel(const float* __restrict
 }
 
 // One block.  offsets[e]: first place of expert e; tiles[k] = (expert, first place, rows);
-// meta[0]: number of tiles.  Leaves counts and fill zero.
+// meta[0]: number of tiles.  Leaves counts and fill zero (the scatter that follows counts the
+// places it hands out in fill).
 __global__ __launch_bounds__(256) void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ fill,
                                                        int* __restrict__ offsets, int* __restrict__ tiles,
                                                        int* __restrict__ meta, int n_experts) {
@@ -234,6 +237,57 @@ __global__ __launch_bounds__(256) void moe_ffn2_kernel(const T* __restrict__ act
   }
 }
 
+// The same two products in bfloat16 on the tensor cores (mma_tile.cuh), float32 accumulation.
+template <bool VEC>
+__global__ __launch_bounds__(128) void moe_ffn1_mma_kernel(const __nv_bfloat16* __restrict__ h, long ldh,
+                                                           const __nv_bfloat16* __restrict__ w_gu,
+                                                           const int* __restrict__ tiles, const int* __restrict__ meta,
+                                                           const int* __restrict__ row_token,
+                                                           __nv_bfloat16* __restrict__ act, long lda, int hidden, int ff,
+                                                           int kind, float alpha, float limit) {
+  __shared__ __align__(16) MmaTileSmem s;
+  __shared__ __align__(16) __nv_bfloat16 up_s[MT_N][MT_LD];
+  __shared__ int tok[MT_M];
+  pdl_begin();
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * MT_N;
+  if (threadIdx.x < MT_M) tok[threadIdx.x] = threadIdx.x < rows ? row_token[row0 + threadIdx.x] : 0;
+  __syncthreads();
+  const __nv_bfloat16* wg = w_gu + (size_t)e * 2 * ff * hidden;
+  const __nv_bfloat16* wu = wg + (size_t)ff * hidden;
+  float acc_g[2][4][4] = {}, acc_u[2][4][4] = {};
+  mma_tile_pair<VEC>(
+      acc_g, acc_u, hidden, [&](int m) { return m < rows ? h + (size_t)tok[m] * ldh : nullptr; },
+      [&](int n) { return n0 + n < ff ? wg + (size_t)(n0 + n) * hidden : nullptr; },
+      [&](int n) { return n0 + n < ff ? wu + (size_t)(n0 + n) * hidden : nullptr; }, s, up_s);
+  mma_for_each(acc_g, [&](int m, int n, int mi, int ni, int c) {
+    if (m < rows && n0 + n < ff)
+      act[(size_t)(row0 + m) * lda + n0 + n] =
+          __float2bfloat16_rn(gated_value(acc_g[mi][ni][c], acc_u[mi][ni][c], kind, alpha, limit));
+  });
+}
+
+template <bool VEC>
+__global__ __launch_bounds__(128) void moe_ffn2_mma_kernel(const __nv_bfloat16* __restrict__ act, long lda,
+                                                           const __nv_bfloat16* __restrict__ w_down,
+                                                           const int* __restrict__ tiles, const int* __restrict__ meta,
+                                                           float* __restrict__ eo, int hidden, int ff) {
+  __shared__ __align__(16) MmaTileSmem s;
+  pdl_begin();
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * MT_N;
+  const __nv_bfloat16* wd = w_down + (size_t)e * hidden * ff;
+  float acc[2][4][4] = {};
+  mma_tile<VEC>(
+      acc, ff, [&](int m) { return m < rows ? act + (size_t)(row0 + m) * lda : nullptr; },
+      [&](int n) { return n0 + n < hidden ? wd + (size_t)(n0 + n) * ff : nullptr; }, s);
+  mma_for_each(acc, [&](int m, int n, int mi, int ni, int c) {
+    if (m < rows && n0 + n < hidden) eo[(size_t)(row0 + m) * hidden + n0 + n] = acc[mi][ni][c];
+  });
+}
+
 // y[t] (+)= sum_j weights[t, j] * eo[place_of[t, j]], j in order.
 __global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restrict__ eo,
                                                           const float* __restrict__ weights,
@@ -273,8 +327,8 @@ RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, i
 }
 
 // The pairs laid out expert by expert: offsets [experts + 1], tiles [max_tiles][3], meta [1],
-// row_token and place_of [tokens * top].  counts as rl_moe_select left it; counts and fill are
-// zero afterwards.  max_tiles >= rl_moe_max_tiles(pairs, experts).
+// row_token and place_of [tokens * top].  counts as rl_moe_select left it, zero afterwards;
+// fill is scratch.  max_tiles >= rl_moe_max_tiles(pairs, experts).
 RL_EXPORT int rl_moe_plan(const int* ids, int* counts, int* fill, int* offsets, int* tiles, int* meta, int* row_token,
                           int* place_of, int n_tokens, int n_experts, int top, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
@@ -312,11 +366,13 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
     rl::launch_pdl(rl::moe_ffn2_kernel<float>, g2, 256, 0, stream, (const float*)act, lda, (const float*)w_down, tiles,
                    meta, eo, hidden, ff);
   } else {
-    rl::launch_pdl(rl::moe_ffn1_kernel<__nv_bfloat16>, g1, 256, 0, stream, (const __nv_bfloat16*)h, ldh,
-                   (const __nv_bfloat16*)w_gu, tiles, meta, row_token, (__nv_bfloat16*)act, lda, hidden, ff, kind,
-                   alpha, limit);
-    rl::launch_pdl(rl::moe_ffn2_kernel<__nv_bfloat16>, g2, 256, 0, stream, (const __nv_bfloat16*)act, lda,
-                   (const __nv_bfloat16*)w_down, tiles, meta, eo, hidden, ff);
+    const bool vec1 = hidden % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)w_gu % 16) == 0;
+    const bool vec2 = ff % 8 == 0 && lda % 8 == 0 && ((uintptr_t)act % 16) == 0 && ((uintptr_t)w_down % 16) == 0;
+    rl::launch_pdl(vec1 ? rl::moe_ffn1_mma_kernel<true> : rl::moe_ffn1_mma_kernel<false>, g1, 128, 0, stream,
+                   (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gu, tiles, meta, row_token,
+                   (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
+    rl::launch_pdl(vec2 ? rl::moe_ffn2_mma_kernel<true> : rl::moe_ffn2_mma_kernel<false>, g2, 128, 0, stream,
+                   (const __nv_bfloat16*)act, lda, (const __nv_bfloat16*)w_down, tiles, meta, eo, hidden, ff);
   }
   rl::launch_pdl(rl::moe_combine_kernel, n_tokens, 256, 0, stream, (const float*)eo, weights, place_of, y, ldy,
                  n_tokens, hidden, top, add);

@@ -159,7 +159,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_latent_decode_fits.argtypes = [I, I, I]
         lib.rl_latent_kv_write.argtypes = [I, P, L, P, F, P, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P]
         lib.rl_latent_q_rope.argtypes = [I, P, L, I, I, P, L, I, I, I, I, P, P, I, I, P]
-        lib.rl_latent_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, P, I, I, I, I, F, P, I, P, I, I, I, P, P, P, P]
+        lib.rl_latent_attention.argtypes = [I, P, L, P, P, I, P, P, P, P, L, P, I, I, I, I, F, P, I, P, I, I, I, P, P, I, P, P]
         lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P]
         lib.rl_gated_act.argtypes = [I, P, L, I, P, L, I, I, I, F, F, P]
         lib.rl_token_gate.argtypes = [I, P, L, P, P, L, I, I, P, L, I, I, I, P, I, P, P]
@@ -1024,12 +1024,14 @@ def latent_q_rope(q, rows, inv_freq, positions, *, n_heads: int, head_in: int, p
 
 def latent_attention(q, pool, block_table, q_start, kv_len, slots, out, *, sink, n_heads: int, rank: int, scale: float,
                      tiles, n_tiles: int, decode_reqs, n_decode: int, decode_by_request: bool = False,
-                     n_splits: int = 1, part_o=None, part_ml=None) -> None:
+                     n_splits: int = 1, part_o=None, part_ml=None, simt_only: bool = False) -> None:
     """Causal attention of the step's query rows ``q`` [tokens, heads * row width] over the cached
     latent rows (``pool`` [pages, 1, 1, page size, row width]); a row's first ``rank`` entries are
     its value; ``out`` [tokens, heads * rank].  ``sink`` float32 [heads] or ``None``.
     ``decode_by_request``: decoded requests take the kernel that serves all heads in one block
-    and cuts a request's keys into ``n_splits`` parts (scratch ``part_o``, ``part_ml``)."""
+    and cuts a request's keys into ``n_splits`` parts (scratch ``part_o``, ``part_ml``).  bfloat16
+    runs on the tensor cores where the sizes fit and decoded requests go by request;
+    ``simt_only`` (for tests and comparisons) keeps it on the CUDA-core kernels."""
     _need(q, "q", contiguous=False)
     _need(pool, "pool", q.dtype)
     _need(out, "out", q.dtype, contiguous=False)
@@ -1048,7 +1050,7 @@ def latent_attention(q, pool, block_table, q_start, kv_len, slots, out, *, sink,
                                     _ptr(q_start), _ptr(kv_len), _ptr(slots), _ptr(out), out.stride(0), _ptr(sink),
                                     n_heads, rank, row_width, page_size, float(scale), _ptr(tiles), n_tiles,
                                     _ptr(decode_reqs), n_decode, int(decode_by_request), n_splits, _ptr(part_o),
-                                    _ptr(part_ml), _ptr(status_word(q.device)), _stream())
+                                    _ptr(part_ml), int(simt_only), _ptr(status_word(q.device)), _stream())
     if rc in (-2, -3):
         raise KernelError(f"latent_attention: sizes not taken (heads {n_heads}, value width {rank}, row width {row_width})")
     _ok(rc, "latent_attention")

@@ -62,6 +62,9 @@ class LatentAttention(Part):
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
+        # W_uk per head as [latent, plain]: the query's product with it then reads both operands
+        # along their inner index, like every other product
+        self.uk_weight = self.uk_weight.view(self.num_heads, self.plain_dim, self.kv_rank).transpose(1, 2).contiguous()
         pad = self.heads_padded - self.heads_width
         if pad:  # the output product reads rows in 16-byte pieces: zero columns fill the last one
             self.o_weight = torch.nn.functional.pad(self.o_weight, (0, pad)).contiguous()
@@ -102,7 +105,7 @@ class LatentAttention(Part):
         # the query rows [q_plain W_uk | rotated part] of every head
         rows = ws.get("latent_q_rows", (n, H * W), act)
         K.head_linear(q, self.uk_weight, rows, n_tokens=n, n_heads=H, k=self.plain_dim, n=rank,
-                      in_strides=(q.stride(0), self.head_in), w_strides=(self.plain_dim * rank, rank, 1),
+                      in_strides=(q.stride(0), self.head_in), w_strides=(self.plain_dim * rank, 1, self.plain_dim),
                       out_strides=(H * W, W))
         K.latent_q_rope(q, rows, freq, ctx.positions, n_heads=H, head_in=self.head_in, plain=self.plain_dim,
                         rank=rank, rot_dim=self.rot_dim, rot_dims=self.rotary.dims, row_width=W)
