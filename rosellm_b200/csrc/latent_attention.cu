@@ -448,7 +448,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   const int W = p.row_width, H = p.n_heads;
   const int Wk = (W + 15) & ~15, LD = Wk + 8, W8 = Wk >> 3;
   bf16* q_s = reinterpret_cast<bf16*>(latent_smem);  // [RB][LD]
-  bf16* k_s = q_s + RB * LD;                         // [LM_KT][LD]
+  bf16* k_s = q_s + RB * LD;                         // [2 stages][LM_KT][LD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   int req, t0 = 0, sp = 0;
@@ -507,25 +507,44 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   const bf16* qa = q_s + (rg * 16 + g) * LD + 2 * t;
   const uint32_t k_s_addr = (uint32_t)__cvta_generic_to_shared(k_s);
 
-  for (int kt = beg; kt < end; kt += LM_KT) {
-    __syncthreads();  // the tile before has been used (first pass: q_s is written)
+  // a tile of keys into stage `st`: valid 16-byte pieces by cp.async, the rest zeros
+  auto stage_keys = [&](int kt, int st) {
+    bf16* dst = k_s + st * LM_KT * LD;
     for (int i = tid; i < LM_KT * W8; i += 128) {
       const int j = i / W8, c = (i - j * W8) * 8;
       const int key = kt + j;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      int page = -1;
       if (key < end && c < W) {
-        const int page = bt[key / p.page_size];
-        if (page < 0)
-          atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        else
-          v = *reinterpret_cast<const uint4*>((const bf16*)p.pool + ((size_t)page * p.page_size + key % p.page_size) * W + c);
+        page = bt[key / p.page_size];
+        if (page < 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
       }
-      *reinterpret_cast<uint4*>(k_s + j * LD + c) = v;
+      if (page >= 0) {
+        const bf16* src = (const bf16*)p.pool + ((size_t)page * p.page_size + key % p.page_size) * W + c;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + j * LD + c)),
+                     "l"(src)
+                     : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst + j * LD + c) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (beg < end) stage_keys(beg, 0);
+  int st = 0;
+  for (int kt = beg; kt < end; kt += LM_KT, st ^= 1) {
+    if (kt + LM_KT < end) {
+      stage_keys(kt + LM_KT, st ^ 1);  // the stage was last read two tiles ago, before that tile's closing barrier
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();  // this tile has landed for every thread (first pass: q_s is written too)
+    const bf16* k_t = k_s + st * LM_KT * LD;
+    const uint32_t k_t_addr = k_s_addr + (uint32_t)(st * LM_KT * LD * 2);
     float s[4][4];
 #pragma unroll
     for (int ni = 0; ni < 4; ++ni) s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f;
+#pragma unroll 2
     for (int ks = 0; ks < Wk; ks += 16) {
       uint32_t a[4];
       a[0] = *reinterpret_cast<const uint32_t*>(qa + ks);
@@ -534,7 +553,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
       a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + ks + 8);
 #pragma unroll
       for (int ni = 0; ni < 4; ++ni) {
-        const bf16* kb = k_s + (ni * 8 + g) * LD + ks + 2 * t;
+        const bf16* kb = k_t + (ni * 8 + g) * LD + ks + 2 * t;
         mma_16x8x16(s[ni], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
       }
     }
@@ -581,7 +600,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
 #pragma unroll
       for (int nv = 0; nv < NVW; nv += 2) {
         const int col = min((vh * NVW + nv + (lane >> 4)) * 8, Wk - 8);
-        const uint32_t addr = k_s_addr + (uint32_t)(((j * 16 + (lane & 15)) * LD + col) * 2);
+        const uint32_t addr = k_t_addr + (uint32_t)(((j * 16 + (lane & 15)) * LD + col) * 2);
         uint32_t b0, b1, b2, b3;
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
@@ -590,6 +609,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
         mma_16x8x16(o[nv + 1], pa, b2, b3);
       }
     }
+    __syncthreads();  // the stage may be written again
   }
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -622,12 +642,14 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   }
 }
 
-template <int NVW, int DVS>
+// DVS_DEC, NVW_DEC: the form of the kernel that decoded tokens take (few heads: the value columns
+// spread over all four warps, so that none of them idles on rows that do not exist).
+template <int NVW, int DVS, int NVW_DEC, int DVS_DEC>
 static inline void launch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                      int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
-  constexpr int RB = 16 * (4 / DVS);
+  constexpr int RB = 16 * (4 / DVS), RB_DEC = 16 * (4 / DVS_DEC);
   const int Wk = (p.row_width + 15) & ~15;
-  const size_t smem = (size_t)(RB + LM_KT) * (Wk + 8) * 2;
+  const size_t smem = (size_t)(RB + 2 * LM_KT) * (Wk + 8) * 2;
   static size_t granted = 0;
   if (smem > 48 * 1024 && smem > granted) {
     cudaFuncSetAttribute(latent_attn_mma_kernel<NVW, DVS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -637,8 +659,15 @@ static inline void launch_latent_mma(const LatentParams& p, const int* tiles, in
     launch_pdl(latent_attn_mma_kernel<NVW, DVS>, dim3(n_tiles, (LT_Q * p.n_heads + RB - 1) / RB), 128, smem, stream, p,
                tiles, decode_reqs, 0, 1, part_o, part_ml);
   if (n_decode > 0) {
-    launch_pdl(latent_attn_mma_kernel<NVW, DVS>, dim3(n_decode, (p.n_heads + RB - 1) / RB, n_splits), 128, smem, stream,
-               p, tiles, decode_reqs, 1, n_splits, part_o, part_ml);
+    const size_t smem_dec = (size_t)(RB_DEC + 2 * LM_KT) * (Wk + 8) * 2;
+    static size_t granted_dec = 0;
+    if (smem_dec > 48 * 1024 && smem_dec > granted_dec) {
+      cudaFuncSetAttribute(latent_attn_mma_kernel<NVW_DEC, DVS_DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem_dec);
+      granted_dec = smem_dec;
+    }
+    launch_pdl(latent_attn_mma_kernel<NVW_DEC, DVS_DEC>, dim3(n_decode, (p.n_heads + RB_DEC - 1) / RB_DEC, n_splits),
+               128, smem_dec, stream, p, tiles, decode_reqs, 1, n_splits, part_o, part_ml);
     if (n_splits > 1)
       launch_pdl(latent_attn_merge_kernel<__nv_bfloat16>, dim3(n_decode, p.n_heads), 64, 0, stream,
                  (const float*)part_o, (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots,
@@ -650,16 +679,22 @@ static inline void launch_latent_mma(const LatentParams& p, const int* tiles, in
 static inline bool dispatch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                        int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   const int Wk = (p.row_width + 15) & ~15;
-  if ((size_t)(64 + LM_KT) * (Wk + 8) * 2 > 200 * 1024 || p.n_heads * LT_Q > 65535 * 16) return false;
+  if ((size_t)(64 + 2 * LM_KT) * (Wk + 8) * 2 > 200 * 1024 || p.n_heads * LT_Q > 65535 * 16) return false;
   const int n8 = (p.rank + 7) / 8;
-#define RL_LATENT_MMA(NVW, DVS) \
-  launch_latent_mma<NVW, DVS>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream)
-  if (n8 <= 2) RL_LATENT_MMA(2, 1);
-  else if (n8 <= 4) RL_LATENT_MMA(4, 1);
-  else if (n8 <= 8) RL_LATENT_MMA(8, 1);
-  else if (n8 <= 16) RL_LATENT_MMA(16, 1);
-  else if (n8 <= 32) RL_LATENT_MMA(32, 1);
-  else if (n8 <= 64) RL_LATENT_MMA(32, 2);
+  // decoded tokens: up to 16 heads are one warp's rows, up to 32 two warps'
+  const bool few = p.n_heads <= 16, some = p.n_heads <= 32;
+#define RL_LATENT_MMA(NVW, DVS, NVW4, NVW2)                                                                              \
+  do {                                                                                                                   \
+    if (few) launch_latent_mma<NVW, DVS, NVW4, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+    else if (some) launch_latent_mma<NVW, DVS, NVW2, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+    else launch_latent_mma<NVW, DVS, NVW, DVS>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+  } while (0)
+  if (n8 <= 2) RL_LATENT_MMA(2, 1, 2, 2);
+  else if (n8 <= 4) RL_LATENT_MMA(4, 1, 2, 2);
+  else if (n8 <= 8) RL_LATENT_MMA(8, 1, 2, 4);
+  else if (n8 <= 16) RL_LATENT_MMA(16, 1, 4, 8);
+  else if (n8 <= 32) RL_LATENT_MMA(32, 1, 8, 16);
+  else if (n8 <= 64) RL_LATENT_MMA(32, 2, 16, 32);
   else return false;
 #undef RL_LATENT_MMA
   return true;

@@ -15,9 +15,10 @@ namespace rl {
 
 constexpr int MT_M = 64, MT_N = 64, MT_K = 32, MT_LD = MT_K + 8;
 
+// Two stages: the next K block of both operands is on its way (cp.async) while this one is used.
 struct MmaTileSmem {
-  __nv_bfloat16 a[MT_M][MT_LD];
-  __nv_bfloat16 b[MT_N][MT_LD];
+  __nv_bfloat16 a[2][MT_M][MT_LD];
+  __nv_bfloat16 b[2][MT_N][MT_LD];
 };
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -28,6 +29,7 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint32_t (
 }
 
 // 64 rows x MT_K elements of an operand into shared memory, zeros beyond k_total and for null rows.
+// VEC: by cp.async (the caller commits and waits); otherwise through registers, element by element.
 template <bool VEC, class Row>
 __device__ __forceinline__ void mma_stage(__nv_bfloat16 (*dst)[MT_LD], Row row, int k0, int k_total) {
   for (int i = threadIdx.x; i < 64 * (MT_K / 8); i += 128) {
@@ -36,7 +38,10 @@ __device__ __forceinline__ void mma_stage(__nv_bfloat16 (*dst)[MT_LD], Row row, 
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (src != nullptr && k0 + kv < k_total) {
       if (VEC) {
-        v = *reinterpret_cast<const uint4*>(src + k0 + kv);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(&dst[m][kv])),
+                     "l"(src + k0 + kv)
+                     : "memory");
+        continue;
       } else {
         __nv_bfloat16 e[8];
 #pragma unroll
@@ -77,15 +82,29 @@ __device__ __forceinline__ void mma_step(float (&acc)[2][4][4], const __nv_bfloa
   }
 }
 
+__device__ __forceinline__ void mma_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void mma_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <bool VEC, class RowA, class RowB>
 __device__ __forceinline__ void mma_tile(float (&acc)[2][4][4], int k_total, RowA row_a, RowB row_b,
                                          MmaTileSmem& s) {
-  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
-    mma_stage<VEC>(s.a, row_a, k0, k_total);
-    mma_stage<VEC>(s.b, row_b, k0, k_total);
+  mma_stage<VEC>(s.a[0], row_a, 0, k_total);
+  mma_stage<VEC>(s.b[0], row_b, 0, k_total);
+  mma_commit();
+  int buf = 0;
+  for (int k0 = 0; k0 < k_total; k0 += MT_K, buf ^= 1) {
+    if (k0 + MT_K < k_total) {
+      mma_stage<VEC>(s.a[buf ^ 1], row_a, k0 + MT_K, k_total);
+      mma_stage<VEC>(s.b[buf ^ 1], row_b, k0 + MT_K, k_total);
+      mma_commit();
+      mma_wait<1>();
+    } else {
+      mma_wait<0>();
+    }
     __syncthreads();
-    mma_step(acc, s.a, s.b);
-    __syncthreads();
+    mma_step(acc, s.a[buf], s.b[buf]);
+    __syncthreads();  // the stage may be written again
   }
 }
 
@@ -93,14 +112,25 @@ __device__ __forceinline__ void mma_tile(float (&acc)[2][4][4], int k_total, Row
 template <bool VEC, class RowA, class RowB, class RowC>
 __device__ __forceinline__ void mma_tile_pair(float (&acc_b)[2][4][4], float (&acc_c)[2][4][4], int k_total,
                                               RowA row_a, RowB row_b, RowC row_c, MmaTileSmem& s,
-                                              __nv_bfloat16 (*c_s)[MT_LD]) {
-  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
-    mma_stage<VEC>(s.a, row_a, k0, k_total);
-    mma_stage<VEC>(s.b, row_b, k0, k_total);
-    mma_stage<VEC>(c_s, row_c, k0, k_total);
+                                              __nv_bfloat16 (*c_s)[MT_N][MT_LD]) {
+  mma_stage<VEC>(s.a[0], row_a, 0, k_total);
+  mma_stage<VEC>(s.b[0], row_b, 0, k_total);
+  mma_stage<VEC>(c_s[0], row_c, 0, k_total);
+  mma_commit();
+  int buf = 0;
+  for (int k0 = 0; k0 < k_total; k0 += MT_K, buf ^= 1) {
+    if (k0 + MT_K < k_total) {
+      mma_stage<VEC>(s.a[buf ^ 1], row_a, k0 + MT_K, k_total);
+      mma_stage<VEC>(s.b[buf ^ 1], row_b, k0 + MT_K, k_total);
+      mma_stage<VEC>(c_s[buf ^ 1], row_c, k0 + MT_K, k_total);
+      mma_commit();
+      mma_wait<1>();
+    } else {
+      mma_wait<0>();
+    }
     __syncthreads();
-    mma_step(acc_b, s.a, s.b);
-    mma_step(acc_c, s.a, c_s);
+    mma_step(acc_b, s.a[buf], s.b[buf]);
+    mma_step(acc_c, s.a[buf], c_s[buf]);
     __syncthreads();
   }
 }

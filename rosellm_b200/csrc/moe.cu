@@ -246,7 +246,7 @@ __global__ __launch_bounds__(128) void moe_ffn1_mma_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ act, long lda, int hidden, int ff,
                                                            int kind, float alpha, float limit) {
   __shared__ __align__(16) MmaTileSmem s;
-  __shared__ __align__(16) __nv_bfloat16 up_s[MT_N][MT_LD];
+  __shared__ __align__(16) __nv_bfloat16 up_s[2][MT_N][MT_LD];
   __shared__ int tok[MT_M];
   pdl_begin();
   if ((int)blockIdx.x >= meta[0]) return;

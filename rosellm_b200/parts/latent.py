@@ -76,11 +76,11 @@ class LatentAttention(Part):
     def decode_plan_for(self, n_decode: int, span: int, act_dtype: torch.dtype = torch.bfloat16) -> tuple[int, bool]:
         """(splits, False): into how many parts the keys of a decoded request are cut, each part a
         block that serves all heads.  Enough parts to give every SM a block, none shorter than
-        128 keys."""
+        64 keys."""
         if n_decode == 0 or not K.latent_decode_fits(self.num_heads, self.kv_rank, self.row_width):
             return 1, False
         sms = K.sm_count()
-        return max(1, min(span // 128, -(-sms // n_decode), 64)), False
+        return max(1, min(span // 64, -(-sms // n_decode), 64)), False
 
     def decode_plan(self, ctx) -> tuple[int, bool]:
         return self.decode_plan_for(ctx.n_decode, ctx.max_kv_len, ctx.act_dtype)

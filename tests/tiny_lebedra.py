@@ -1,6 +1,6 @@
 """Small Lebedra configurations for the tests, and helpers to write them as model folders.
 
-X and Y differ from one another in every size and option, and avoid coincidences: the plain
+X, Y and Z differ from one another in every size and option, and avoid coincidences: the plain
 and rotated query parts have different sizes, value and latent sizes differ from both, head
 counts are odd, a group keeps more than one of several groups, inner sizes and the token
 input's size are no multiples of 8, and one layer has no feed-forward.
@@ -44,9 +44,20 @@ RAW_Y = {
         {"type": "latent_attention", "mixer": mixer(7, 8, 2, 8, 16, 0.5, 50.0), "mlp": {"kind": "dense", "ff": 72}},
     ],
 }
+# Sizes that are multiples of nothing convenient: per-head sizes of 12, 6 and 10, a latent of 18,
+# five experts, an inner size of 36 and 12, a token input of 5 entries, a prime vocabulary.
+RAW_Z = {
+    "architecture": "Lebedra", "vocab": 131, "width": 72, "residual_mult": 0.3, "norm": {"eps": 1e-4},
+    "token_side": {"dim": 5},
+    "layers": [
+        {"type": "latent_attention", "mixer": mixer(3, 12, 6, 10, 18, 0.4, 20.0), "mlp": moe(12, 1.0, 5, 2)},
+        {"type": "latent_attention", "mixer": mixer(9, 4, 10, 6, 30, 0.35, 7.0), "mlp": {"kind": "dense", "ff": 36}},
+    ],
+}
 TINY = {
     "X": dict(raw=RAW_X, seed=11, std=0.2, page_size=16),
     "Y": dict(raw=RAW_Y, seed=12, std=0.25, page_size=8),
+    "Z": dict(raw=RAW_Z, seed=13, std=0.2, page_size=32),
 }
 
 
