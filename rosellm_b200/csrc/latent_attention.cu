@@ -414,7 +414,6 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part_o, const
 // accumulator layout into A fragments and adds P V, V being the first `rank` columns of the
 // same tile, fetched transposed with ldmatrix.  A warp holds NVW value tiles of 8 columns;
 // latents beyond 256 entries are split over two warps that share their rows (DVS = 2).
-constexpr int LM_KT = 32;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ void mma_16x8x16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -436,13 +435,13 @@ __device__ __forceinline__ float quad_sum(float v) {
   return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
-template <int NVW, int DVS>
+template <int NVW, int DVS, int NKT>
 __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, const int* __restrict__ tiles,
                                                               const int* __restrict__ decode_reqs, int decode,
                                                               int n_splits, float* __restrict__ part_o,
                                                               float* __restrict__ part_ml) {
   using bf16 = __nv_bfloat16;
-  constexpr int RB = 16 * (4 / DVS);
+  constexpr int RB = 16 * (4 / DVS), LM_KT = 8 * NKT;
   extern __shared__ __align__(16) unsigned char latent_smem[];
   pdl_begin();
   const int W = p.row_width, H = p.n_heads;
@@ -504,7 +503,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   float o[NVW][4];
 #pragma unroll
   for (int i = 0; i < NVW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const bf16* qa = q_s + (rg * 16 + g) * LD + 2 * t;
+  const uint32_t q_s_addr = (uint32_t)__cvta_generic_to_shared(q_s);
   const uint32_t k_s_addr = (uint32_t)__cvta_generic_to_shared(k_s);
 
   // a tile of keys into stage `st`: valid 16-byte pieces by cp.async, the rest zeros
@@ -539,28 +538,34 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();  // this tile has landed for every thread (first pass: q_s is written too)
-    const bf16* k_t = k_s + st * LM_KT * LD;
     const uint32_t k_t_addr = k_s_addr + (uint32_t)(st * LM_KT * LD * 2);
-    float s[4][4];
+    float s[NKT][4];
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni) s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f;
+    for (int ni = 0; ni < NKT; ++ni) s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f;
+    // fragments by ldmatrix, four 8 x 8 pieces an instruction: of Q (rows, k), (rows + 8, k),
+    // (rows, k + 8), (rows + 8, k + 8); of the keys (keys, k), (keys, k + 8), (keys + 8, k), (keys + 8, k + 8)
+    const uint32_t qa_addr = q_s_addr + (uint32_t)(((rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8) * 2);
+    const uint32_t kb_addr = k_t_addr + (uint32_t)((((lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8) * 2);
 #pragma unroll 2
     for (int ks = 0; ks < Wk; ks += 16) {
       uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(qa + ks);
-      a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + ks);
-      a[2] = *reinterpret_cast<const uint32_t*>(qa + ks + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + ks + 8);
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                   : "r"(qa_addr + (uint32_t)(ks * 2)));
 #pragma unroll
-      for (int ni = 0; ni < 4; ++ni) {
-        const bf16* kb = k_t + (ni * 8 + g) * LD + ks + 2 * t;
-        mma_16x8x16(s[ni], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+      for (int ni = 0; ni < NKT; ni += 2) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(kb_addr + (uint32_t)((ni * 8 * LD + ks) * 2)));
+        mma_16x8x16(s[ni], a, b0, b1);
+        mma_16x8x16(s[ni + 1], a, b2, b3);
       }
     }
     // mask by each row's own position, online softmax in base 2
     float top_a = -CUDART_INF_F, top_b = -CUDART_INF_F;
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni)
+    for (int ni = 0; ni < NKT; ++ni)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = kt + ni * 8 + 2 * t + (c & 1);
@@ -573,7 +578,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
     const float alpha_b = new_b == -CUDART_INF_F ? 1.f : exp2f(m_b - new_b);
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni)
+    for (int ni = 0; ni < NKT; ++ni)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float top = c < 2 ? new_a : new_b;
@@ -591,7 +596,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
     }
     // P as A fragments of two steps of 16 keys, then O += P V with V read transposed
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < NKT / 2; ++j) {
       uint32_t pa[4];
       pa[0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
       pa[1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
@@ -644,29 +649,39 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
 
 // DVS_DEC, NVW_DEC: the form of the kernel that decoded tokens take (few heads: the value columns
 // spread over all four warps, so that none of them idles on rows that do not exist).
-template <int NVW, int DVS, int NVW_DEC, int DVS_DEC>
+template <int NVW, int DVS, int NKT, int NVW_DEC, int DVS_DEC>
 static inline void launch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                      int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
-  constexpr int RB = 16 * (4 / DVS), RB_DEC = 16 * (4 / DVS_DEC);
+  constexpr int RB = 16 * (4 / DVS), RB_DEC = 16 * (4 / DVS_DEC), LM_KT = 8 * NKT, KT_DEC = 32;
   const int Wk = (p.row_width + 15) & ~15;
   const size_t smem = (size_t)(RB + 2 * LM_KT) * (Wk + 8) * 2;
   static size_t granted = 0;
   if (smem > 48 * 1024 && smem > granted) {
-    cudaFuncSetAttribute(latent_attn_mma_kernel<NVW, DVS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NVW, DVS, NKT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     granted = smem;
   }
+  // Prompt portions run for hundreds of microseconds and want every block the registers allow:
+  // with the common half-and-half split of an SM's memory only one block of 76 KB fits (measured:
+  // 4 warps an SM, 0.22 instructions issued a cycle and scheduler), so this form asks for all of
+  // it as shared memory.
+  static bool carved = false;
+  if (!carved) {
+    cudaFuncSetAttribute(latent_attn_mma_kernel<NVW, DVS, NKT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         (int)cudaSharedmemCarveoutMaxShared);
+    carved = true;
+  }
   if (n_tiles > 0)
-    launch_pdl(latent_attn_mma_kernel<NVW, DVS>, dim3(n_tiles, (LT_Q * p.n_heads + RB - 1) / RB), 128, smem, stream, p,
+    launch_pdl_split(false, latent_attn_mma_kernel<NVW, DVS, NKT>, dim3(n_tiles, (LT_Q * p.n_heads + RB - 1) / RB), 128, smem, stream, p,
                tiles, decode_reqs, 0, 1, part_o, part_ml);
   if (n_decode > 0) {
-    const size_t smem_dec = (size_t)(RB_DEC + 2 * LM_KT) * (Wk + 8) * 2;
+    const size_t smem_dec = (size_t)(RB_DEC + 2 * KT_DEC) * (Wk + 8) * 2;
     static size_t granted_dec = 0;
     if (smem_dec > 48 * 1024 && smem_dec > granted_dec) {
-      cudaFuncSetAttribute(latent_attn_mma_kernel<NVW_DEC, DVS_DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaFuncSetAttribute(latent_attn_mma_kernel<NVW_DEC, DVS_DEC, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem_dec);
       granted_dec = smem_dec;
     }
-    launch_pdl(latent_attn_mma_kernel<NVW_DEC, DVS_DEC>, dim3(n_decode, (p.n_heads + RB_DEC - 1) / RB_DEC, n_splits),
+    launch_pdl(latent_attn_mma_kernel<NVW_DEC, DVS_DEC, 4>, dim3(n_decode, (p.n_heads + RB_DEC - 1) / RB_DEC, n_splits),
                128, smem_dec, stream, p, tiles, decode_reqs, 1, n_splits, part_o, part_ml);
     if (n_splits > 1)
       launch_pdl(latent_attn_merge_kernel<__nv_bfloat16>, dim3(n_decode, p.n_heads), 64, 0, stream,
@@ -675,26 +690,36 @@ static inline void launch_latent_mma(const LatentParams& p, const int* tiles, in
   }
 }
 
+static int latent_prefill_form = 0;
+
 // The tensor-core kernel for these sizes, or false when it does not take them.
 static inline bool dispatch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                        int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   const int Wk = (p.row_width + 15) & ~15;
-  if ((size_t)(64 + 2 * LM_KT) * (Wk + 8) * 2 > 200 * 1024 || p.n_heads * LT_Q > 65535 * 16) return false;
+  if (p.n_heads * LT_Q > 65535 * 16) return false;
   const int n8 = (p.rank + 7) / 8;
+  // shared memory of the form the rule below picks: its rows of queries and two stages of keys
+  const int rows = n8 > 32 ? 32 : 64, keys = n8 <= 16 ? 64 : 32;
+  if ((size_t)(rows + 2 * keys) * (Wk + 8) * 2 > 200 * 1024) return false;
   // decoded tokens: up to 16 heads are one warp's rows, up to 32 two warps'
   const bool few = p.n_heads <= 16, some = p.n_heads <= 32;
-#define RL_LATENT_MMA(NVW, DVS, NVW4, NVW2)                                                                              \
+#define RL_LATENT_MMA(NVW, DVS, NKT, NVW4, NVW2)                                                                         \
   do {                                                                                                                   \
-    if (few) launch_latent_mma<NVW, DVS, NVW4, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
-    else if (some) launch_latent_mma<NVW, DVS, NVW2, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
-    else launch_latent_mma<NVW, DVS, NVW, DVS>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+    if (few) launch_latent_mma<NVW, DVS, NKT, NVW4, 4>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+    else if (some) launch_latent_mma<NVW, DVS, NKT, NVW2, 2>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
+    else launch_latent_mma<NVW, DVS, NKT, NVW, DVS>(p, tiles, n_tiles, decode_reqs, n_decode, n_splits, part_o, part_ml, stream); \
   } while (0)
-  if (n8 <= 2) RL_LATENT_MMA(2, 1, 2, 2);
-  else if (n8 <= 4) RL_LATENT_MMA(4, 1, 2, 2);
-  else if (n8 <= 8) RL_LATENT_MMA(8, 1, 2, 4);
-  else if (n8 <= 16) RL_LATENT_MMA(16, 1, 4, 8);
-  else if (n8 <= 32) RL_LATENT_MMA(32, 1, 8, 16);
-  else if (n8 <= 64) RL_LATENT_MMA(32, 2, 16, 32);
+  // latent_prefill_form (for measurements): 0 the rule below; 1: latents of 129 to 256 with their
+  // value columns over two warps; 2: the same with key tiles of 64
+  if (n8 <= 2) RL_LATENT_MMA(2, 1, 8, 2, 2);
+  else if (n8 <= 4) RL_LATENT_MMA(4, 1, 8, 2, 2);
+  else if (n8 <= 8) RL_LATENT_MMA(8, 1, 8, 2, 4);
+  else if (n8 <= 16) RL_LATENT_MMA(16, 1, 8, 4, 8);
+  else if (n8 <= 32 && latent_prefill_form == 1) RL_LATENT_MMA(16, 2, 4, 8, 16);
+  else if (n8 <= 32 && latent_prefill_form == 2 && (size_t)(32 + 128) * (Wk + 8) * 2 <= 200 * 1024)
+    RL_LATENT_MMA(16, 2, 8, 8, 16);
+  else if (n8 <= 32) RL_LATENT_MMA(32, 1, 4, 8, 16);
+  else if (n8 <= 64) RL_LATENT_MMA(32, 2, 4, 16, 32);
   else return false;
 #undef RL_LATENT_MMA
   return true;
@@ -744,6 +769,9 @@ static inline int dispatch_latent(const LatentParams& p, const int* tiles, int n
 
 // How many bytes of shared memory the kernels above may ask for.
 static constexpr size_t LATENT_SMEM_LIMIT = 200 * 1024;
+
+// Which form of the tensor-core kernel prompt portions take (measurements; 0: the default rule).
+RL_EXPORT void rl_latent_prefill_form(int form) { rl::latent_prefill_form = form; }
 
 // 1 if the sizes fit the kernels (value width up to 512, shared memory), else 0.
 RL_EXPORT int rl_latent_attention_fits(int n_heads, int rank, int row_width) {

@@ -15,10 +15,12 @@ namespace rl {
 
 constexpr int MT_M = 64, MT_N = 64, MT_K = 32, MT_LD = MT_K + 8;
 
-// Two stages: the next K block of both operands is on its way (cp.async) while this one is used.
+// Three stages: the next two K blocks of both operands are on their way (cp.async) while this
+// one is used.
+constexpr int MT_STAGES = 3;
 struct MmaTileSmem {
-  __nv_bfloat16 a[2][MT_M][MT_LD];
-  __nv_bfloat16 b[2][MT_N][MT_LD];
+  __nv_bfloat16 a[MT_STAGES][MT_M][MT_LD];
+  __nv_bfloat16 b[MT_STAGES][MT_N][MT_LD];
 };
 
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -26,6 +28,12 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint32_t (
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"((uint32_t)__cvta_generic_to_shared(row)));
 }
 
 // 64 rows x MT_K elements of an operand into shared memory, zeros beyond k_total and for null rows.
@@ -56,24 +64,21 @@ __device__ __forceinline__ void mma_stage(__nv_bfloat16 (*dst)[MT_LD], Row row, 
 __device__ __forceinline__ void mma_step(float (&acc)[2][4][4], const __nv_bfloat16 (*a_s)[MT_LD],
                                          const __nv_bfloat16 (*b_s)[MT_LD]) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
   const int m0 = (warp >> 1) * 32, n0 = (warp & 1) * 32;
 #pragma unroll
   for (int kk = 0; kk < MT_K; kk += 16) {
     uint32_t af[2][4], bf[4][2];
+    // four 8 x 8 pieces an instruction: A as (rows, k), (rows + 8, k), (rows, k + 8), (rows + 8, k + 8);
+    // B (stored [n][k]) as (n, k), (n, k + 8), (n + 8, k), (n + 8, k + 8)
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi) {
-      const int r = m0 + mi * 16 + g;
-      af[mi][0] = *reinterpret_cast<const uint32_t*>(&a_s[r][kk + 2 * t]);
-      af[mi][1] = *reinterpret_cast<const uint32_t*>(&a_s[r + 8][kk + 2 * t]);
-      af[mi][2] = *reinterpret_cast<const uint32_t*>(&a_s[r][kk + 2 * t + 8]);
-      af[mi][3] = *reinterpret_cast<const uint32_t*>(&a_s[r + 8][kk + 2 * t + 8]);
+      const __nv_bfloat16* pa = &a_s[m0 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8];
+      ldmatrix_x4(af[mi][0], af[mi][1], af[mi][2], af[mi][3], pa);
     }
 #pragma unroll
-    for (int ni = 0; ni < 4; ++ni) {
-      const int c = n0 + ni * 8 + g;
-      bf[ni][0] = *reinterpret_cast<const uint32_t*>(&b_s[c][kk + 2 * t]);
-      bf[ni][1] = *reinterpret_cast<const uint32_t*>(&b_s[c][kk + 2 * t + 8]);
+    for (int ni = 0; ni < 4; ni += 2) {
+      const __nv_bfloat16* pb = &b_s[n0 + ni * 8 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8];
+      ldmatrix_x4(bf[ni][0], bf[ni][1], bf[ni + 1][0], bf[ni + 1][1], pb);
     }
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
@@ -86,25 +91,33 @@ __device__ __forceinline__ void mma_commit() { asm volatile("cp.async.commit_gro
 template <int N>
 __device__ __forceinline__ void mma_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// One commit group a K block, also where a block does not exist (an empty group): so "all but
+// the newest MT_STAGES - 1 groups are complete" always means "this iteration's block has landed".
 template <bool VEC, class RowA, class RowB>
 __device__ __forceinline__ void mma_tile(float (&acc)[2][4][4], int k_total, RowA row_a, RowB row_b,
                                          MmaTileSmem& s) {
-  mma_stage<VEC>(s.a[0], row_a, 0, k_total);
-  mma_stage<VEC>(s.b[0], row_b, 0, k_total);
-  mma_commit();
-  int buf = 0;
-  for (int k0 = 0; k0 < k_total; k0 += MT_K, buf ^= 1) {
-    if (k0 + MT_K < k_total) {
-      mma_stage<VEC>(s.a[buf ^ 1], row_a, k0 + MT_K, k_total);
-      mma_stage<VEC>(s.b[buf ^ 1], row_b, k0 + MT_K, k_total);
-      mma_commit();
-      mma_wait<1>();
-    } else {
-      mma_wait<0>();
+#pragma unroll
+  for (int st = 0; st < MT_STAGES - 1; ++st) {
+    if (st * MT_K < k_total) {
+      mma_stage<VEC>(s.a[st], row_a, st * MT_K, k_total);
+      mma_stage<VEC>(s.b[st], row_b, st * MT_K, k_total);
     }
+    mma_commit();
+  }
+  int buf = 0, fill = MT_STAGES - 1;
+  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
+    const int ahead = k0 + (MT_STAGES - 1) * MT_K;
+    if (ahead < k_total) {  // into the stage that the iteration before has finished with
+      mma_stage<VEC>(s.a[fill], row_a, ahead, k_total);
+      mma_stage<VEC>(s.b[fill], row_b, ahead, k_total);
+    }
+    mma_commit();
+    mma_wait<MT_STAGES - 1>();
     __syncthreads();
     mma_step(acc, s.a[buf], s.b[buf]);
     __syncthreads();  // the stage may be written again
+    buf = buf + 1 == MT_STAGES ? 0 : buf + 1;
+    fill = fill + 1 == MT_STAGES ? 0 : fill + 1;
   }
 }
 
@@ -113,25 +126,31 @@ template <bool VEC, class RowA, class RowB, class RowC>
 __device__ __forceinline__ void mma_tile_pair(float (&acc_b)[2][4][4], float (&acc_c)[2][4][4], int k_total,
                                               RowA row_a, RowB row_b, RowC row_c, MmaTileSmem& s,
                                               __nv_bfloat16 (*c_s)[MT_N][MT_LD]) {
-  mma_stage<VEC>(s.a[0], row_a, 0, k_total);
-  mma_stage<VEC>(s.b[0], row_b, 0, k_total);
-  mma_stage<VEC>(c_s[0], row_c, 0, k_total);
-  mma_commit();
-  int buf = 0;
-  for (int k0 = 0; k0 < k_total; k0 += MT_K, buf ^= 1) {
-    if (k0 + MT_K < k_total) {
-      mma_stage<VEC>(s.a[buf ^ 1], row_a, k0 + MT_K, k_total);
-      mma_stage<VEC>(s.b[buf ^ 1], row_b, k0 + MT_K, k_total);
-      mma_stage<VEC>(c_s[buf ^ 1], row_c, k0 + MT_K, k_total);
-      mma_commit();
-      mma_wait<1>();
-    } else {
-      mma_wait<0>();
+#pragma unroll
+  for (int st = 0; st < MT_STAGES - 1; ++st) {
+    if (st * MT_K < k_total) {
+      mma_stage<VEC>(s.a[st], row_a, st * MT_K, k_total);
+      mma_stage<VEC>(s.b[st], row_b, st * MT_K, k_total);
+      mma_stage<VEC>(c_s[st], row_c, st * MT_K, k_total);
     }
+    mma_commit();
+  }
+  int buf = 0, fill = MT_STAGES - 1;
+  for (int k0 = 0; k0 < k_total; k0 += MT_K) {
+    const int ahead = k0 + (MT_STAGES - 1) * MT_K;
+    if (ahead < k_total) {
+      mma_stage<VEC>(s.a[fill], row_a, ahead, k_total);
+      mma_stage<VEC>(s.b[fill], row_b, ahead, k_total);
+      mma_stage<VEC>(c_s[fill], row_c, ahead, k_total);
+    }
+    mma_commit();
+    mma_wait<MT_STAGES - 1>();
     __syncthreads();
     mma_step(acc_b, s.a[buf], s.b[buf]);
     mma_step(acc_c, s.a[buf], c_s[buf]);
     __syncthreads();
+    buf = buf + 1 == MT_STAGES ? 0 : buf + 1;
+    fill = fill + 1 == MT_STAGES ? 0 : fill + 1;
   }
 }
 

@@ -246,7 +246,7 @@ __global__ __launch_bounds__(128) void moe_ffn1_mma_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ act, long lda, int hidden, int ff,
                                                            int kind, float alpha, float limit) {
   __shared__ __align__(16) MmaTileSmem s;
-  __shared__ __align__(16) __nv_bfloat16 up_s[2][MT_N][MT_LD];
+  __shared__ __align__(16) __nv_bfloat16 up_s[MT_STAGES][MT_N][MT_LD];
   __shared__ int tok[MT_M];
   pdl_begin();
   if ((int)blockIdx.x >= meta[0]) return;
@@ -368,11 +368,23 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
   } else {
     const bool vec1 = hidden % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)w_gu % 16) == 0;
     const bool vec2 = ff % 8 == 0 && lda % 8 == 0 && ((uintptr_t)act % 16) == 0 && ((uintptr_t)w_down % 16) == 0;
-    rl::launch_pdl(vec1 ? rl::moe_ffn1_mma_kernel<true> : rl::moe_ffn1_mma_kernel<false>, g1, 128, 0, stream,
-                   (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gu, tiles, meta, row_token,
-                   (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
-    rl::launch_pdl(vec2 ? rl::moe_ffn2_mma_kernel<true> : rl::moe_ffn2_mma_kernel<false>, g2, 128, 0, stream,
-                   (const __nv_bfloat16*)act, lda, (const __nv_bfloat16*)w_down, tiles, meta, eo, hidden, ff);
+    auto k1 = vec1 ? rl::moe_ffn1_mma_kernel<true> : rl::moe_ffn1_mma_kernel<false>;
+    auto k2 = vec2 ? rl::moe_ffn2_mma_kernel<true> : rl::moe_ffn2_mma_kernel<false>;
+    // three stages of three operands are 46 KB a block: with the common half-and-half split of an
+    // SM's memory two blocks fit, with all of it as shared memory four (the registers' limit)
+    static bool carved[4] = {false, false, false, false};
+    if (!carved[vec1]) {
+      cudaFuncSetAttribute(k1, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+      carved[vec1] = true;
+    }
+    if (!carved[2 + vec2]) {
+      cudaFuncSetAttribute(k2, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+      carved[2 + vec2] = true;
+    }
+    rl::launch_pdl_split(false, k1, g1, 128, 0, stream, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gu, tiles,
+                         meta, row_token, (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
+    rl::launch_pdl_split(false, k2, g2, 128, 0, stream, (const __nv_bfloat16*)act, lda, (const __nv_bfloat16*)w_down,
+                         tiles, meta, eo, hidden, ff);
   }
   rl::launch_pdl(rl::moe_combine_kernel, n_tokens, 256, 0, stream, (const float*)eo, weights, place_of, y, ldy,
                  n_tokens, hidden, top, add);

@@ -33,6 +33,9 @@ __global__ __launch_bounds__(256) void rmsnorm_store_kernel(const float* __restr
 }
 
 // stream[i] += mult * rmsnorm(y[i]) * gamma; copy[i] = bfloat16(stream[i]) when copy is given.
+// VEC: widths and row strides are multiples of 4 and every row starts on a 16-byte boundary
+// (8-byte for the copy): 16-byte loads and stores.
+template <bool VEC>
 __global__ __launch_bounds__(256) void rmsnorm_add_kernel(const float* __restrict__ y, long ldy,
                                                           const float* __restrict__ gamma, float* __restrict__ stream,
                                                           long lds, __nv_bfloat16* __restrict__ copy, long ldc,
@@ -42,17 +45,44 @@ __global__ __launch_bounds__(256) void rmsnorm_add_kernel(const float* __restric
   const int i = blockIdx.x;
   if (i >= n_rows) return;
   const float* yr = y + (size_t)i * ldy;
+  float* xr = stream + (size_t)i * lds;
   float s = 0.f;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) {
-    const float v = yr[d];
-    s = fmaf(v, v, s);
+  if (VEC) {
+    const float4* y4 = reinterpret_cast<const float4*>(yr);
+    for (int d = threadIdx.x; d < width / 4; d += blockDim.x) {
+      const float4 v = y4[d];
+      s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s))));
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) s = fmaf(yr[d], yr[d], s);
   }
   const float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)width + eps);
-  float* xr = stream + (size_t)i * lds;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) {
-    const float v = xr[d] + mult * (yr[d] * r * gamma[d]);
-    xr[d] = v;
-    if (copy != nullptr) copy[(size_t)i * ldc + d] = __float2bfloat16_rn(v);
+  if (VEC) {
+    const float4* y4 = reinterpret_cast<const float4*>(yr);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    float4* x4 = reinterpret_cast<float4*>(xr);
+    for (int d = threadIdx.x; d < width / 4; d += blockDim.x) {
+      const float4 v = y4[d], g = g4[d];
+      float4 x = x4[d];
+      x.x += mult * (v.x * r * g.x);
+      x.y += mult * (v.y * r * g.y);
+      x.z += mult * (v.z * r * g.z);
+      x.w += mult * (v.w * r * g.w);
+      x4[d] = x;
+      if (copy != nullptr) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(copy + (size_t)i * ldc + 4 * d) = packed;
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+      const float v = xr[d] + mult * (yr[d] * r * gamma[d]);
+      xr[d] = v;
+      if (copy != nullptr) copy[(size_t)i * ldc + d] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -91,8 +121,10 @@ RL_EXPORT int rl_rmsnorm_add(const float* y, long ldy, const float* gamma, float
                              long ldc, int n_rows, int width, float eps, float mult, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (width <= 0) return -2;
-  rl::launch_pdl(rl::rmsnorm_add_kernel, n_rows, rl::norm_threads(width), 0, stream, y, ldy, gamma, stream_rows, lds,
-                 (__nv_bfloat16*)copy, ldc, n_rows, width, eps, mult);
+  const bool vec = width % 4 == 0 && ldy % 4 == 0 && lds % 4 == 0 && ldc % 4 == 0 && (uintptr_t)y % 16 == 0 &&
+                   (uintptr_t)stream_rows % 16 == 0 && (uintptr_t)gamma % 16 == 0 && (uintptr_t)copy % 8 == 0;
+  rl::launch_pdl(vec ? rl::rmsnorm_add_kernel<true> : rl::rmsnorm_add_kernel<false>, n_rows, rl::norm_threads(width), 0,
+                 stream, y, ldy, gamma, stream_rows, lds, (__nv_bfloat16*)copy, ldc, n_rows, width, eps, mult);
   RL_CHECK_LAUNCH();
   return 0;
 }
