@@ -373,32 +373,50 @@ __global__ __launch_bounds__(32 * LD_WARPS) void latent_attn_decode_kernel(
   }
 }
 
-// out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the splits, in their order.
+// out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s over the parts, in their order.  The parts'
+// weights e^{m_s - M} / sum are worked out once a block (at most 64 parts), then every thread sums
+// its columns.
 template <typename T>
-__global__ void latent_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         int n_splits, const int* __restrict__ decode_reqs,
-                                         const int* __restrict__ q_start, const int* __restrict__ slots,
-                                         T* __restrict__ out, long out_stride, int n_heads, int rank) {
+__global__ __launch_bounds__(128) void latent_attn_merge_kernel(const float* __restrict__ part_o,
+                                                                const float* __restrict__ part_ml, int n_splits,
+                                                                const int* __restrict__ decode_reqs,
+                                                                const int* __restrict__ q_start,
+                                                                const int* __restrict__ slots, T* __restrict__ out,
+                                                                long out_stride, int n_heads, int rank) {
+  __shared__ float w_s[64];
   pdl_begin();
   const int di = blockIdx.x, h = blockIdx.y;
   const int req = decode_reqs[di];
-  if (slots[req] < 0) return;  // written by the decode kernel
+  if (slots[req] < 0) return;  // written by the attention kernel
   const size_t row0 = ((size_t)di * n_heads + h) * n_splits;
-  float top = -CUDART_INF_F;
-  for (int s = 0; s < n_splits; ++s) top = fmaxf(top, part_ml[2 * (row0 + s)]);
-  float den = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part_ml[2 * (row0 + s)];
-    den += (ms == -CUDART_INF_F ? 0.f : expf(ms - top)) * part_ml[2 * (row0 + s) + 1];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;
+    if (lane < n_splits) {
+      m0 = part_ml[2 * (row0 + lane)];
+      l0 = part_ml[2 * (row0 + lane) + 1];
+    }
+    if (lane + 32 < n_splits) {
+      m1 = part_ml[2 * (row0 + lane + 32)];
+      l1 = part_ml[2 * (row0 + lane + 32) + 1];
+    }
+    const float top = warp_max(fmaxf(m0, m1));
+    const float e0 = m0 == -CUDART_INF_F ? 0.f : expf(m0 - top), e1 = m1 == -CUDART_INF_F ? 0.f : expf(m1 - top);
+    // the denominator in the parts' order: lane by lane
+    float den = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float term = s < 32 ? __shfl_sync(0xffffffffu, e0 * l0, s) : __shfl_sync(0xffffffffu, e1 * l1, s - 32);
+      den += term;
+    }
+    const float inv = 1.0f / den;
+    w_s[lane] = e0 * inv;
+    w_s[lane + 32] = e1 * inv;
   }
-  const float inv = 1.0f / den;
+  __syncthreads();
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[2 * (row0 + s)];
-      if (ms != -CUDART_INF_F) acc = fmaf(expf(ms - top), part_o[(row0 + s) * rank + d], acc);
-    }
-    out[(size_t)q_start[req] * out_stride + (size_t)h * rank + d] = from_f32<T>(acc * inv);
+    for (int s = 0; s < n_splits; ++s) acc = fmaf(w_s[s], part_o[(row0 + s) * rank + d], acc);
+    out[(size_t)q_start[req] * out_stride + (size_t)h * rank + d] = from_f32<T>(acc);
   }
 }
 
@@ -684,7 +702,7 @@ static inline void launch_latent_mma(const LatentParams& p, const int* tiles, in
     launch_pdl(latent_attn_mma_kernel<NVW_DEC, DVS_DEC, 4>, dim3(n_decode, (p.n_heads + RB_DEC - 1) / RB_DEC, n_splits),
                128, smem_dec, stream, p, tiles, decode_reqs, 1, n_splits, part_o, part_ml);
     if (n_splits > 1)
-      launch_pdl(latent_attn_merge_kernel<__nv_bfloat16>, dim3(n_decode, p.n_heads), 64, 0, stream,
+      launch_pdl(latent_attn_merge_kernel<__nv_bfloat16>, dim3(n_decode, p.n_heads), 128, 0, stream,
                  (const float*)part_o, (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots,
                  (__nv_bfloat16*)p.out, p.out_stride, p.n_heads, p.rank);
   }
@@ -745,7 +763,7 @@ static inline void launch_latent(const LatentParams& p, const int* tiles, int n_
     launch_pdl(latent_attn_decode_kernel<T, NCHUNK>, dim3(n_decode, n_splits), 32 * LD_WARPS, smem, stream, p,
                decode_reqs, n_splits, part_o, part_ml);
     if (n_splits > 1)
-      launch_pdl(latent_attn_merge_kernel<T>, dim3(n_decode, p.n_heads), 64, 0, stream, (const float*)part_o,
+      launch_pdl(latent_attn_merge_kernel<T>, dim3(n_decode, p.n_heads), 128, 0, stream, (const float*)part_o,
                  (const float*)part_ml, n_splits, decode_reqs, p.q_start, p.slots, (T*)p.out, p.out_stride, p.n_heads,
                  p.rank);
   }
@@ -843,8 +861,8 @@ RL_EXPORT int rl_latent_attention(int dtype, const void* q, long q_stride, const
                                   int simt_only, int* status, cudaStream_t stream) {
   if (!rl_latent_attention_fits(n_heads, rank, row_width) || status == nullptr) return -2;
   if (decode_by_request && !rl_latent_decode_fits(n_heads, rank, row_width)) return -3;
-  if (n_splits < 1 || n_splits > 65535 || (decode_by_request && n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
-    return -4;
+  if (n_splits < 1 || n_splits > 64 || (decode_by_request && n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
+    return -4;  // the merge takes up to 64 parts
   rl::LatentParams p{q, q_stride, pool, block_table, bt_stride, q_start, kv_len, slots, out, out_stride, sink,
                      n_heads, rank, row_width, page_size, scale, status};
   int rc = 0;
