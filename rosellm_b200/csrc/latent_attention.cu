@@ -470,8 +470,11 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   const int g = lane >> 2, t = lane & 3;
   int req, t0 = 0, sp = 0;
   if (!decode) {
-    req = tiles[2 * blockIdx.x];
-    t0 = tiles[2 * blockIdx.x + 1];
+    // the list runs from a request's first tile to its last, which walks the most keys: blocks take
+    // it from the back, so that the long ones start first and the short ones fill the SMs' last round
+    const int tile = gridDim.y - 1 - blockIdx.y;  // prompt portions: grid (chunks of rows, tiles)
+    req = tiles[2 * tile];
+    t0 = tiles[2 * tile + 1];
   } else {
     req = decode_reqs[blockIdx.x];
     sp = blockIdx.z;
@@ -479,7 +482,7 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
   const int qs = p.q_start[req];
   const int q_len = p.q_start[req + 1] - qs;
   const int rows_total = (decode ? 1 : min(LT_Q, q_len - t0)) * H;
-  const int row0 = blockIdx.y * RB;
+  const int row0 = (decode ? blockIdx.y : blockIdx.x) * RB;
   if (row0 >= rows_total) return;
   bf16* out = (bf16*)p.out;
   const int slot = p.slots[req];
@@ -689,7 +692,7 @@ static inline void launch_latent_mma(const LatentParams& p, const int* tiles, in
     carved = true;
   }
   if (n_tiles > 0)
-    launch_pdl_split(false, latent_attn_mma_kernel<NVW, DVS, NKT>, dim3(n_tiles, (LT_Q * p.n_heads + RB - 1) / RB), 128, smem, stream, p,
+    launch_pdl_split(false, latent_attn_mma_kernel<NVW, DVS, NKT>, dim3((LT_Q * p.n_heads + RB - 1) / RB, n_tiles), 128, smem, stream, p,
                tiles, decode_reqs, 0, 1, part_o, part_ml);
   if (n_decode > 0) {
     const size_t smem_dec = (size_t)(RB_DEC + 2 * KT_DEC) * (Wk + 8) * 2;
@@ -714,7 +717,7 @@ static int latent_prefill_form = 0;
 static inline bool dispatch_latent_mma(const LatentParams& p, const int* tiles, int n_tiles, const int* decode_reqs,
                                        int n_decode, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
   const int Wk = (p.row_width + 15) & ~15;
-  if (p.n_heads * LT_Q > 65535 * 16) return false;
+  if (n_tiles > 65535) return false;
   const int n8 = (p.rank + 7) / 8;
   // shared memory of the form the rule below picks: its rows of queries and two stages of keys
   const int rows = n8 > 32 ? 32 : 64, keys = n8 <= 16 ? 64 : 32;

@@ -14,10 +14,12 @@
 // `moe_combine_kernel` sums a token's expert outputs in the order of its choices, times their
 // weights (a fixed order: the result does not depend on where the pairs were placed).
 // Products: float32 as IEEE multiply-adds on 64 x 64 tiles (tile_gemm.cuh); bfloat16 on the tensor
-// cores (mma_tile.cuh) with float32 accumulation.
+// cores (mma_tile.cuh) with float32 accumulation, or, where an expert has a few rows only (decode
+// steps), by `moe_rows_kernel`, which streams the weights once with a warp an output column.
 #include <math_constants.h>
 
 #include "gated_act.cuh"
+#include "gemm_vec.cuh"
 #include "mma_tile.cuh"
 #include "tile_gemm.cuh"
 
@@ -288,6 +290,76 @@ __global__ __launch_bounds__(128) void moe_ffn2_mma_kernel(const __nv_bfloat16* 
   });
 }
 
+// Few rows an expert (a decode step): nothing is left of a 64-row tile but its weights, so the
+// weights are streamed instead.  A warp owns one output column of its tile's expert: it reads the
+// column's weight row (gate and up rows with PAIR) once, 16 bytes a lane a step, against up to
+// MOE_ROWS_PASS input rows held in shared memory, and reduces over the lanes; tiles with more
+// rows take further passes (their weights then come from L2).  float32 accumulation.
+constexpr int MOE_ROWS_PASS = 4;
+
+template <bool PAIR>
+__global__ __launch_bounds__(256) void moe_rows_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                       const __nv_bfloat16* __restrict__ w,
+                                                       const int* __restrict__ tiles, const int* __restrict__ meta,
+                                                       const int* __restrict__ row_token,
+                                                       __nv_bfloat16* __restrict__ act, long lda,
+                                                       float* __restrict__ eo, int k_total, int n_total, int kind,
+                                                       float alpha, float limit) {
+  extern __shared__ __align__(16) __nv_bfloat16 rows_s[];  // [MOE_ROWS_PASS][k_total]
+  pdl_begin();
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.y * 8 + warp;
+  // PAIR: w is [experts][2][n_total][k_total] (gate rows, then up rows); else [experts][n_total][k_total]
+  const __nv_bfloat16* w0 = w + ((size_t)e * (PAIR ? 2 : 1) * n_total + min(n, n_total - 1)) * k_total;
+  const __nv_bfloat16* w1 = w0 + (size_t)n_total * k_total;
+  const int k8 = k_total >> 3;
+  for (int r0 = 0; r0 < rows; r0 += MOE_ROWS_PASS) {
+    const int nr = min(MOE_ROWS_PASS, rows - r0);
+    __syncthreads();  // the rows of the pass before have been used
+    for (int i = threadIdx.x; i < nr * k8; i += blockDim.x) {
+      const int r = i / k8, c = (i - r * k8) * 8;
+      const int src = PAIR ? row_token[row0 + r0 + r] : row0 + r0 + r;
+      *reinterpret_cast<uint4*>(rows_s + (size_t)r * k_total + c) = *reinterpret_cast<const uint4*>(x + (size_t)src * ldx + c);
+    }
+    __syncthreads();
+    float a0[MOE_ROWS_PASS], a1[MOE_ROWS_PASS];
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PASS; ++r) a0[r] = a1[r] = 0.f;
+#pragma unroll 2
+    for (int c = lane * 8; c < k_total; c += 256) {
+      float wv0[8], wv1[8];
+      Vec16<__nv_bfloat16>::load(w0 + c, wv0);
+      if (PAIR) Vec16<__nv_bfloat16>::load(w1 + c, wv1);
+#pragma unroll
+      for (int r = 0; r < MOE_ROWS_PASS; ++r) {
+        if (r < nr) {
+          float xv[8];
+          Vec16<__nv_bfloat16>::load(rows_s + (size_t)r * k_total + c, xv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            a0[r] = fmaf(wv0[j], xv[j], a0[r]);
+            if (PAIR) a1[r] = fmaf(wv1[j], xv[j], a1[r]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PASS; ++r) {
+      if (r >= nr) continue;
+      const float s0 = warp_sum(a0[r]);
+      const float s1 = PAIR ? warp_sum(a1[r]) : 0.f;
+      if (lane == 0 && n < n_total) {
+        if (PAIR)
+          act[(size_t)(row0 + r0 + r) * lda + n] = __float2bfloat16_rn(gated_value(s0, s1, kind, alpha, limit));
+        else
+          eo[(size_t)(row0 + r0 + r) * n_total + n] = s0;
+      }
+    }
+  }
+}
+
 // y[t] (+)= sum_j weights[t, j] * eo[place_of[t, j]], j in order.
 __global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restrict__ eo,
                                                           const float* __restrict__ weights,
@@ -368,6 +440,21 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
   } else {
     const bool vec1 = hidden % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)w_gu % 16) == 0;
     const bool vec2 = ff % 8 == 0 && lda % 8 == 0 && ((uintptr_t)act % 16) == 0 && ((uintptr_t)w_down % 16) == 0;
+    // few pairs an expert (decode steps; on average one pass of rows each): stream the weights, a warp an
+    // output column.  Measured at 32 experts, top 4: 8 requests 0.997 -> 0.843 ms a step, but 64 requests (8
+    // rows an expert, two passes and more) 1.57 -> 2.16 ms, hence the bound
+    const bool few = (long)n_tokens * top <= (long)rl::MOE_ROWS_PASS * n_experts && vec1 && vec2 && (size_t)hidden * 8 <= 48 * 1024 &&
+                     (size_t)ff * 8 <= 48 * 1024;
+    if (few) {
+      rl::launch_pdl(rl::moe_rows_kernel<true>, dim3(max_tiles, (ff + 7) / 8), 256,
+                     (size_t)rl::MOE_ROWS_PASS * hidden * 2, stream, (const __nv_bfloat16*)h, ldh,
+                     (const __nv_bfloat16*)w_gu, tiles, meta, row_token, (__nv_bfloat16*)act, lda, (float*)nullptr,
+                     hidden, ff, kind, alpha, limit);
+      rl::launch_pdl(rl::moe_rows_kernel<false>, dim3(max_tiles, (hidden + 7) / 8), 256,
+                     (size_t)rl::MOE_ROWS_PASS * ff * 2, stream, (const __nv_bfloat16*)act, lda,
+                     (const __nv_bfloat16*)w_down, tiles, meta, row_token, (__nv_bfloat16*)nullptr, 0L, eo, ff, hidden,
+                     kind, alpha, limit);
+    } else {
     auto k1 = vec1 ? rl::moe_ffn1_mma_kernel<true> : rl::moe_ffn1_mma_kernel<false>;
     auto k2 = vec2 ? rl::moe_ffn2_mma_kernel<true> : rl::moe_ffn2_mma_kernel<false>;
     // three stages of three operands are 46 KB a block: with the common half-and-half split of an
@@ -385,6 +472,7 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
                          meta, row_token, (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
     rl::launch_pdl_split(false, k2, g2, 128, 0, stream, (const __nv_bfloat16*)act, lda, (const __nv_bfloat16*)w_down,
                          tiles, meta, eo, hidden, ff);
+    }
   }
   rl::launch_pdl(rl::moe_combine_kernel, n_tokens, 256, 0, stream, (const float*)eo, weights, place_of, y, ldy,
                  n_tokens, hidden, top, add);
