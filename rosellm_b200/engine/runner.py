@@ -88,6 +88,8 @@ def _layout(n_tokens: int, n_reqs: int, n_rows: int, n_decode: int, n_tiles: int
 
 
 class ModelRunner:
+    DEFAULT_POOL_CONTEXT = 8192  # tokens a sequence that the default pool is sized for (see __init__)
+
     def __init__(self, config: ModelConfig, file_tensors: dict[str, torch.Tensor],
                  engine_config: EngineConfig | None = None, source: str = "<tensors>") -> None:
         self.config = config
@@ -105,11 +107,19 @@ class ModelRunner:
         self.model = Model(self.spec, self.dtype, self.device)
         self.model.load_tensors(file_tensors, source)
         kv_specs, state_specs = self.model.kv_specs(), self.model.state_specs()
+        longest = min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions)
+        pool_tokens = ec.kv_cache_tokens
+        if (ec.num_pages is None and pool_tokens is None and ec.gpu_memory_utilization is None
+                and ec.kv_cache_mem_fraction is None and longest > self.DEFAULT_POOL_CONTEXT):
+            # a model without a position table may run to any length: by default the pool is not
+            # made for max_num_seqs sequences of that length, but of DEFAULT_POOL_CONTEXT tokens
+            # (a longer request takes more of the pool; the scheduler preempts when pages run out)
+            pool_tokens = ec.max_num_seqs * self.DEFAULT_POOL_CONTEXT
         self.cache_plan = plan = plan_cache(
             page_size=ec.page_size, max_num_seqs=ec.max_num_seqs,
-            max_model_len=min(ec.max_model_len or self.spec.max_positions, self.spec.max_positions),
+            max_model_len=longest,
             bytes_per_token=kv_bytes_per_token(kv_specs, ec.dtype),
-            num_pages=ec.num_pages, kv_cache_tokens=ec.kv_cache_tokens,
+            num_pages=ec.num_pages, kv_cache_tokens=pool_tokens,
             gpu_memory_utilization=ec.gpu_memory_utilization, kv_cache_mem_fraction=ec.kv_cache_mem_fraction,
             mem_get_info=lambda: torch.cuda.mem_get_info(self.device),
             reserve_bytes=self._bytes_beside_the_cache(state_specs),

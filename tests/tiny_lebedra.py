@@ -1,6 +1,6 @@
 """Small Lebedra configurations for the tests, and helpers to write them as model folders.
 
-X, Y and Z differ from one another in every size and option, and avoid coincidences: the plain
+X, Y, Z and W differ from one another in every size and option, and avoid coincidences: the plain
 and rotated query parts have different sizes, value and latent sizes differ from both, head
 counts are odd, a group keeps more than one of several groups, inner sizes and the token
 input's size are no multiples of 8, and one layer has no feed-forward.
@@ -54,10 +54,23 @@ RAW_Z = {
         {"type": "latent_attention", "mixer": mixer(9, 4, 10, 6, 30, 0.35, 7.0), "mlp": {"kind": "dense", "ff": 36}},
     ],
 }
+# A wider one: six and twelve heads, latents of 96 and 128, eight experts, a layer without a
+# feed-forward in the middle.
+RAW_W = {
+    "architecture": "Lebedra", "vocab": 2000, "width": 384, "residual_mult": 0.4, "norm": {"eps": 1e-5},
+    "token_side": {"dim": 40},
+    "layers": [
+        {"type": "latent_attention", "mixer": mixer(6, 48, 16, 56, 96, 0.11, 1e4), "mlp": {"kind": "dense", "ff": 640}},
+        {"type": "latent_attention", "mixer": mixer(6, 48, 16, 56, 96, 0.11, 1e4), "mlp": moe(256, 2.0, 8, 2, 4, 2)},
+        {"type": "latent_attention", "mixer": mixer(12, 32, 32, 32, 128, 0.1, 5e5), "mlp": None},
+        {"type": "latent_attention", "mixer": mixer(6, 48, 16, 56, 96, 0.11, 1e4), "mlp": moe(192, 1.0, 8, 3, 2, 2)},
+    ],
+}
 TINY = {
     "X": dict(raw=RAW_X, seed=11, std=0.2, page_size=16),
     "Y": dict(raw=RAW_Y, seed=12, std=0.25, page_size=8),
     "Z": dict(raw=RAW_Z, seed=13, std=0.2, page_size=32),
+    "W": dict(raw=RAW_W, seed=14, std=0.08, page_size=16),
 }
 
 
