@@ -567,8 +567,13 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
     // (rows, k + 8), (rows + 8, k + 8); of the keys (keys, k), (keys, k + 8), (keys + 8, k), (keys + 8, k + 8)
     const uint32_t qa_addr = q_s_addr + (uint32_t)(((rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8) * 2);
     const uint32_t kb_addr = k_t_addr + (uint32_t)((((lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8) * 2);
-#pragma unroll 2
-    for (int ks = 0; ks < Wk; ks += 16) {
+    // two sets of accumulators take the K steps in turn: every step adds into the accumulators of
+    // the step before last, so twice as many independent mma chains are in flight (the kernel's
+    // first stall reason was the fixed latency between dependent mma instructions)
+    float s2[NKT][4];
+#pragma unroll
+    for (int ni = 0; ni < NKT; ++ni) s2[ni][0] = s2[ni][1] = s2[ni][2] = s2[ni][3] = 0.f;
+    auto score_step = [&](int ks, float (&acc)[NKT][4]) {
       uint32_t a[4];
       asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                    : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
@@ -579,10 +584,20 @@ __global__ __launch_bounds__(128) void latent_attn_mma_kernel(LatentParams p, co
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                      : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
                      : "r"(kb_addr + (uint32_t)((ni * 8 * LD + ks) * 2)));
-        mma_16x8x16(s[ni], a, b0, b1);
-        mma_16x8x16(s[ni + 1], a, b2, b3);
+        mma_16x8x16(acc[ni], a, b0, b1);
+        mma_16x8x16(acc[ni + 1], a, b2, b3);
       }
+    };
+    int ks = 0;
+    for (; ks + 32 <= Wk; ks += 32) {
+      score_step(ks, s);
+      score_step(ks + 16, s2);
     }
+    if (ks < Wk) score_step(ks, s);
+#pragma unroll
+    for (int ni = 0; ni < NKT; ++ni)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[ni][c] += s2[ni][c];
     // mask by each row's own position, online softmax in base 2
     float top_a = -CUDART_INF_F, top_b = -CUDART_INF_F;
 #pragma unroll
