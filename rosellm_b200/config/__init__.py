@@ -13,6 +13,7 @@ from .base import (
 from .engine import EngineConfig
 from .gpt2 import GPT2Config
 from .lebedra import LebedraConfig
+from .porovik import PorovikConfig
 
 __all__ = [
     "Architecture",
@@ -20,6 +21,7 @@ __all__ = [
     "EngineConfig",
     "GPT2Config",
     "LebedraConfig",
+    "PorovikConfig",
     "ModelConfig",
     "load_config",
     "parse_config",

@@ -1,0 +1,325 @@
+// Causal attention with a distance bias, a query temperature, key and value sizes of their own, grouped
+// key/value heads and an output gate, over a paged cache that keeps one row a token and key/value head:
+// [key (dk entries) | value (dv entries)], the value at entry `v_at`.
+//
+//   score(i, j) = (q_i . k_j) * scale * temp(i) - slope_h * (i - j),  j <= i
+//   temp(i)     = 1 + temp_coef * ln(floor((i + 1) / temp_every) + 1)          (temp_every = 0: 1)
+//   slope_h     : a table the caller gives, one entry a head                    (absent: no bias)
+//   out         = softmax(score) V * sigmoid(gate)                             (gate absent: no gate)
+//
+// Scores, softmax and the weighted sums are float32 whatever the cache holds.  Queries and gate logits are
+// float32 columns of the layer's packed projections.
+//
+// `bias_kv_store_kernel` writes a step's keys and values into their pages and mixes the values on the way:
+// v <- (1 - lambda) v + lambda v_src with v_src the values that an earlier layer computed for the same tokens
+// (that layer leaves them in a float32 buffer: mode "source"); what is cached is the mixed value.
+//
+// `bias_attn_kernel`: rows of a block are (token, head) pairs that share a key/value head, so a key tile
+// fetched once serves all of a group's heads; 32 rows x 32 keys a round, online softmax, float32 on the CUDA
+// cores.  A decoded token is a tile of one token.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace rl {
+
+constexpr int BA_ROWS = 32, BA_KEYS = 32, BA_THREADS = 128;
+
+struct BiasAttnParams {
+  const float* q;  // [tokens, ldq]; head h at columns [h * dk, (h + 1) * dk)
+  long ldq;
+  const float* gate;  // [tokens, ldg] logits, head h at [h * dv, ...); or null
+  long ldg;
+  const void* pool;  // [pages, 1, n_kv, page_size, row]
+  const int* block_table;
+  long ldt;
+  const int *q_start, *kv_len, *slots, *tiles, *decode_reqs;
+  void* out;  // [tokens, ldo], head h at [h * dv, ...)
+  long ldo;
+  int n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages;
+  int n_tiles, tile_tokens, tokens_per_block, heads_per_block, n_decode;
+  float scale, temp_coef;
+  int temp_every;
+  const float* slopes;  // [n_heads] or null
+  int* status;
+};
+
+template <typename T, int DVC, typename TOut>
+__global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnParams p) {
+  extern __shared__ __align__(16) float ba_s[];
+  pdl_begin();
+  const int subs = p.tile_tokens / p.tokens_per_block;
+  int req, first;  // the request and the first of its new tokens that this block takes
+  if ((int)blockIdx.x < p.n_tiles * subs) {
+    const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
+    req = p.tiles[2 * tile];
+    first = p.tiles[2 * tile + 1] + sub * p.tokens_per_block;
+  } else {
+    req = p.decode_reqs[blockIdx.x - p.n_tiles * subs];
+    first = 0;
+  }
+  const int slot = p.slots[req];
+  const int t_begin = p.q_start[req], n_new = p.q_start[req + 1] - t_begin;
+  if (slot < 0 || first >= n_new) return;
+  const int n_tok = min(p.tokens_per_block, n_new - first);
+  const int pos0 = p.kv_len[req] - n_new + first;  // position of the block's first token
+  const int g = blockIdx.y, hg = p.n_heads / p.n_kv;
+  const int hb0 = blockIdx.z * p.heads_per_block;
+  const int HB = p.heads_per_block;
+  const int dk = p.dk, dv = p.dv;
+  const int ldq_s = dk | 1, ldk_s = dk | 1, ldv_s = 8 * DVC;
+  float* Qs = ba_s;                        // [BA_ROWS][ldq_s]
+  float* Ks = Qs + BA_ROWS * ldq_s;        // [BA_KEYS][ldk_s]
+  float* Vs = Ks + BA_KEYS * ldk_s;        // [BA_KEYS][ldv_s]
+  float* Ps = Vs + BA_KEYS * ldv_s;        // [BA_ROWS][BA_KEYS + 1]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ty = tid >> 3, tx = tid & 7;
+  // queries
+  for (int r = warp; r < BA_ROWS; r += BA_THREADS / 32) {
+    const int tl = r / HB, hl = r - tl * HB;
+    const bool ok = tl < n_tok && hb0 + hl < hg;
+    const float* src = p.q + (size_t)(t_begin + first + tl) * p.ldq + (size_t)(g * hg + hb0 + hl) * dk;
+    for (int d = lane; d < dk; d += 32) Qs[r * ldq_s + d] = ok ? src[d] : 0.f;
+  }
+  int row_pos[2], row_head[2];
+  float row_mul[2], row_slope[2], m[2], l[2];
+  bool row_ok[2];
+  float acc[2][DVC];
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+    const int r = ty * 2 + a, tl = r / HB, hl = r - tl * HB;
+    row_ok[a] = tl < n_tok && hb0 + hl < hg;
+    row_pos[a] = pos0 + tl;
+    row_head[a] = g * hg + hb0 + hl;
+    float temp = 1.0f;
+    if (p.temp_every > 0) temp = 1.0f + p.temp_coef * logf((float)((row_pos[a] + 1) / p.temp_every + 1));
+    row_mul[a] = p.scale * temp;
+    row_slope[a] = (p.slopes != nullptr && row_ok[a]) ? p.slopes[row_head[a]] : 0.f;
+    m[a] = -CUDART_INF_F;
+    l[a] = 0.f;
+#pragma unroll
+    for (int c = 0; c < DVC; ++c) acc[a][c] = 0.f;
+  }
+  const int last_pos = pos0 + n_tok - 1;
+  const T* pool = reinterpret_cast<const T*>(p.pool);
+  const int* table = p.block_table + (size_t)slot * p.ldt;
+  for (int j0 = 0; j0 <= last_pos; j0 += BA_KEYS) {
+    __syncthreads();  // the tile before has been used (and, the first time, the queries are in place)
+    for (int jj = warp; jj < BA_KEYS; jj += BA_THREADS / 32) {
+      const int j = j0 + jj;
+      const T* src = nullptr;
+      if (j <= last_pos) {
+        const int lp = j / p.page_size;
+        const int page = lp < p.max_pages ? table[lp] : -1;
+        if (page < 0) {
+          if (lane == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        } else {
+          src = pool + (((size_t)page * p.n_kv + g) * p.page_size + (j - lp * p.page_size)) * p.row;
+        }
+      }
+      for (int d = lane; d < dk; d += 32) Ks[jj * ldk_s + d] = src != nullptr ? to_f32(src[d]) : 0.f;
+      for (int c = lane; c < ldv_s; c += 32) Vs[jj * ldv_s + c] = (src != nullptr && c < dv) ? to_f32(src[p.v_at + c]) : 0.f;
+    }
+    __syncthreads();
+    float s[2][4] = {};
+    const float* q0 = Qs + (ty * 2) * ldq_s;
+    const float* q1 = q0 + ldq_s;
+    const float* kb = Ks + tx * ldk_s;
+#pragma unroll 4
+    for (int d = 0; d < dk; ++d) {
+      const float a0 = q0[d], a1 = q1[d];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float kv = kb[b * 8 * ldk_s + d];
+        s[0][b] = fmaf(a0, kv, s[0][b]);
+        s[1][b] = fmaf(a1, kv, s[1][b]);
+      }
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      float tile_max = -CUDART_INF_F;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = j0 + tx + 8 * b;
+        const bool see = row_ok[a] && j <= row_pos[a];
+        s[a][b] = see ? s[a][b] * row_mul[a] - row_slope[a] * (float)(row_pos[a] - j) : -CUDART_INF_F;
+        tile_max = fmaxf(tile_max, s[a][b]);
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
+      const float m_new = fmaxf(m[a], tile_max);
+      const float corr = m[a] == -CUDART_INF_F ? 0.f : expf(m[a] - m_new);
+      float sum = 0.f;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const float pr = s[a][b] == -CUDART_INF_F ? 0.f : expf(s[a][b] - m_new);
+        Ps[(ty * 2 + a) * (BA_KEYS + 1) + tx + 8 * b] = pr;
+        sum += pr;
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      l[a] = l[a] * corr + sum;
+      m[a] = m_new;
+#pragma unroll
+      for (int c = 0; c < DVC; ++c) acc[a][c] *= corr;
+    }
+    __syncwarp();  // a row's probabilities are written and read by the eight threads of one warp
+    const float* p0 = Ps + (ty * 2) * (BA_KEYS + 1);
+    const float* p1 = p0 + (BA_KEYS + 1);
+#pragma unroll 4
+    for (int jj = 0; jj < BA_KEYS; ++jj) {
+      const float w0 = p0[jj], w1 = p1[jj];
+      const float* vr = Vs + jj * ldv_s + tx;
+#pragma unroll
+      for (int c = 0; c < DVC; ++c) {
+        const float v = vr[8 * c];
+        acc[0][c] = fmaf(w0, v, acc[0][c]);
+        acc[1][c] = fmaf(w1, v, acc[1][c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+    if (!row_ok[a]) continue;
+    const int tok = t_begin + first + (ty * 2 + a) / HB;
+    const float inv = 1.0f / l[a];
+    TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)row_head[a] * dv;
+    const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)row_head[a] * dv : nullptr;
+#pragma unroll
+    for (int c = 0; c < DVC; ++c) {
+      const int col = tx + 8 * c;
+      if (col < dv) {
+        float v = acc[a][c] * inv;
+        if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col]));
+        o[col] = from_f32<TOut>(v);
+      }
+    }
+  }
+}
+
+// mix: 0 values as they are; 1 also left in v_src (this layer is the source); 2 mixed with v_src by *lambda.
+template <typename T>
+__global__ void bias_kv_store_kernel(const float* __restrict__ k, long ldk, const float* __restrict__ v, long ldv,
+                                     float* __restrict__ v_src, const float* __restrict__ lambda, int mix,
+                                     T* __restrict__ pool, const int* __restrict__ block_table, long ldt,
+                                     const int* __restrict__ positions, const int* __restrict__ req_of_token,
+                                     const int* __restrict__ slots, int n_tokens, int n_kv, int dk, int dv, int v_at,
+                                     int row, int page_size, int max_pages, int* __restrict__ status) {
+  pdl_begin();
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  const int slot = slots[req_of_token[n]];
+  if (slot < 0) return;
+  const int pos = positions[n], lp = pos / page_size;
+  const int page = (pos >= 0 && lp < max_pages) ? block_table[(size_t)slot * ldt + lp] : -1;
+  const float lam = mix == 2 ? *lambda : 0.f;
+  for (int i = threadIdx.x; i < n_kv * dv; i += blockDim.x) {  // the source is left even where the page is missing
+    float val = v[(size_t)n * ldv + i];
+    if (mix == 1) v_src[(size_t)n * n_kv * dv + i] = val;
+    if (mix == 2) val = (1.0f - lam) * val + lam * v_src[(size_t)n * n_kv * dv + i];
+    if (page >= 0) {
+      const int g = i / dv, c = i - g * dv;
+      pool[(((size_t)page * n_kv + g) * page_size + (pos - lp * page_size)) * row + v_at + c] = from_f32<T>(val);
+    }
+  }
+  if (page < 0) {
+    if (threadIdx.x == 0) atomicOr(status, pos < 0 || lp >= max_pages ? RL_STATUS_BAD_POSITION : RL_STATUS_BAD_PAGE);
+    return;
+  }
+  for (int i = threadIdx.x; i < n_kv * dk; i += blockDim.x) {
+    const int g = i / dk, c = i - g * dk;
+    pool[(((size_t)page * n_kv + g) * page_size + (pos - lp * page_size)) * row + c] = from_f32<T>(k[(size_t)n * ldk + i]);
+  }
+}
+
+template <typename T, int DVC, typename TOut>
+static void launch_bias_attn(const BiasAttnParams& p, dim3 grid, cudaStream_t stream) {
+  const size_t smem = ((size_t)BA_ROWS * (p.dk | 1) + (size_t)BA_KEYS * (p.dk | 1) + (size_t)BA_KEYS * 8 * DVC +
+                       (size_t)BA_ROWS * (BA_KEYS + 1)) * sizeof(float);
+  auto kernel = bias_attn_kernel<T, DVC, TOut>;
+  if (smem > 48 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      raised = true;
+    }
+  }
+  launch_pdl(kernel, grid, BA_THREADS, smem, stream, p);
+}
+
+template <typename T, typename TOut>
+static void dispatch_bias_attn(const BiasAttnParams& p, dim3 grid, cudaStream_t stream) {
+  if (p.dv <= 32) launch_bias_attn<T, 4, TOut>(p, grid, stream);
+  else if (p.dv <= 64) launch_bias_attn<T, 8, TOut>(p, grid, stream);
+  else if (p.dv <= 128) launch_bias_attn<T, 16, TOut>(p, grid, stream);
+  else launch_bias_attn<T, 32, TOut>(p, grid, stream);
+}
+
+}  // namespace rl
+
+// How a block's 32 rows are cut into tokens and heads for `heads_per_group` query heads a key/value head:
+// heads a block (at most 32) and tokens a block (a power of two, at most 32).
+RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int* heads_per_block, int* tokens_per_block) {
+  if (heads_per_group <= 0) return -2;
+  const int hb = heads_per_group < rl::BA_ROWS ? heads_per_group : rl::BA_ROWS;
+  int tt = 1;
+  while (tt * 2 * hb <= rl::BA_ROWS) tt *= 2;
+  *heads_per_block = hb;
+  *tokens_per_block = tt;
+  return 0;
+}
+
+// tiles: (request, first new token) of portions cut every `tile_tokens` tokens (a multiple of the tokens a
+// block takes); decode_reqs: the requests that bring one token.  cache_dtype: the pool's element type;
+// out_dtype: that of out.
+RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, long ldq, const float* gate, long ldg,
+                                const void* pool, const int* block_table, long ldt, const int* q_start,
+                                const int* kv_len, const int* slots, const int* tiles, int n_tiles, int tile_tokens,
+                                const int* decode_reqs, int n_decode, void* out, long ldo, int n_heads, int n_kv, int dk,
+                                int dv, int v_at, int row, int page_size, int max_pages, float scale, float temp_coef,
+                                int temp_every, const float* slopes, int* status, cudaStream_t stream) {
+  if (n_tiles <= 0 && n_decode <= 0) return 0;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || v_at < dk ||
+      v_at + dv > row || n_kv > 65535)
+    return -2;
+  int hb, tt;
+  rl_bias_attention_shape(n_heads / n_kv, &hb, &tt);
+  if (n_tiles > 0 && (tile_tokens < tt || tile_tokens % tt)) return -3;
+  if (n_tiles <= 0) tile_tokens = tt;
+  rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
+                       n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
+                       tt, hb, n_decode > 0 ? n_decode : 0, scale, temp_coef, temp_every, slopes, status};
+  const int head_blocks = (n_heads / n_kv + hb - 1) / hb;
+  const dim3 grid(p.n_tiles * (tile_tokens / tt) + p.n_decode, n_kv, head_blocks);
+  if (cache_dtype == RL_F32) {
+    if (out_dtype == RL_F32) rl::dispatch_bias_attn<float, float>(p, grid, stream);
+    else rl::dispatch_bias_attn<float, __nv_bfloat16>(p, grid, stream);
+  } else {
+    if (out_dtype == RL_F32) rl::dispatch_bias_attn<__nv_bfloat16, float>(p, grid, stream);
+    else rl::dispatch_bias_attn<__nv_bfloat16, __nv_bfloat16>(p, grid, stream);
+  }
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// The step's keys and values (float32 columns of the packed projections) into their pages; see the kernel.
+RL_EXPORT int rl_bias_kv_store(int cache_dtype, const float* k, long ldk, const float* v, long ldv, float* v_src,
+                               const float* lambda, int mix, void* pool, const int* block_table, long ldt,
+                               const int* positions, const int* req_of_token, const int* slots, int n_tokens, int n_kv,
+                               int dk, int dv, int v_at, int row, int page_size, int max_pages, int* status,
+                               cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (mix < 0 || mix > 2 || (mix != 0 && v_src == nullptr) || (mix == 2 && lambda == nullptr) || v_at < dk ||
+      v_at + dv > row)
+    return -2;
+  if (cache_dtype == RL_F32)
+    rl::launch_pdl(rl::bias_kv_store_kernel<float>, n_tokens, 128, 0, stream, k, ldk, v, ldv, v_src, lambda, mix,
+                   (float*)pool, block_table, ldt, positions, req_of_token, slots, n_tokens, n_kv, dk, dv, v_at, row,
+                   page_size, max_pages, status);
+  else
+    rl::launch_pdl(rl::bias_kv_store_kernel<__nv_bfloat16>, n_tokens, 128, 0, stream, k, ldk, v, ldv, v_src, lambda,
+                   mix, (__nv_bfloat16*)pool, block_table, ldt, positions, req_of_token, slots, n_tokens, n_kv, dk, dv,
+                   v_at, row, page_size, max_pages, status);
+  RL_CHECK_LAUNCH();
+  return 0;
+}

@@ -175,6 +175,91 @@ RL_EXPORT int rl_embed(int dtype, const int* ids, const int* pos, const void* ta
 
 namespace rl {
 
+// Token row + a row of a second table chosen by the pair (previous token, token) + position row:
+//   pair row = (prev * mul_prev + token * mul_cur) mod buckets, or row `buckets` (the table's last)
+//   for a sequence's first token.
+// The previous token of a portion's first token comes from the request's state slot (`last_token`,
+// one int32 a slot), which the block of that first token also brings up to date with the portion's
+// last token: no other block of the step touches the slot's entry.  Rows of padding requests
+// (slot < 0) are zero.
+template <typename T>
+__global__ void embed_pair_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
+                                  const int* __restrict__ req_of_token, const int* __restrict__ q_start,
+                                  const int* __restrict__ slots, const T* __restrict__ table,
+                                  const T* __restrict__ pos_table, const T* __restrict__ pair_table,
+                                  float* __restrict__ out, int n_tokens, int hidden, int vocab, int n_positions,
+                                  int buckets, int mul_prev, int mul_cur, int* __restrict__ last_token,
+                                  int* __restrict__ status, const int* __restrict__ feedback, int n_feedback) {
+  __shared__ int prev_s;
+  pdl_begin();
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  float* o = out + (size_t)n * hidden;
+  const int req = req_of_token[n], slot = slots[req];
+  auto resolve = [&](int id) {
+    if (id < 0 && feedback != nullptr && -id - 1 < n_feedback) id = feedback[-id - 1];
+    return id;
+  };
+  const int id = resolve(ids[n]);
+  const int ps = pos[n];
+  const bool bad_id = id < 0 || id >= vocab, bad_pos = ps < 0 || (pos_table != nullptr && ps >= n_positions);
+  if (slot < 0 || bad_id || bad_pos) {
+    if (threadIdx.x == 0 && slot >= 0) atomicOr(status, bad_id ? RL_STATUS_BAD_TOKEN : RL_STATUS_BAD_POSITION);
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) o[d] = 0.f;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    const int first = q_start[req];
+    int prev = 0;
+    if (n == first) {
+      prev = last_token[slot];
+      last_token[slot] = resolve(ids[q_start[req + 1] - 1]);
+    } else {
+      prev = resolve(ids[n - 1]);
+    }
+    prev_s = prev;
+  }
+  __syncthreads();
+  long long pair = buckets;
+  if (ps > 0) {
+    pair = ((long long)prev_s * mul_prev + (long long)id * mul_cur) % buckets;
+    if (pair < 0) pair += buckets;
+  }
+  const T* e = table + (size_t)id * hidden;
+  const T* b = pair_table + (size_t)pair * hidden;
+  const T* p = pos_table != nullptr ? pos_table + (size_t)ps * hidden : nullptr;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float v = to_f32(e[d]) + to_f32(b[d]);
+    if (p != nullptr) v += to_f32(p[d]);
+    o[d] = v;
+  }
+}
+
+}  // namespace rl
+
+RL_EXPORT int rl_embed_pair(int dtype, const int* ids, const int* pos, const int* req_of_token, const int* q_start,
+                            const int* slots, const void* table, const void* pos_table, const void* pair_table,
+                            float* out, int n_tokens, int hidden, int vocab, int n_positions, int buckets,
+                            int mul_prev, int mul_cur, int* last_token, int* status, const int* feedback,
+                            int n_feedback, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (buckets <= 0) return -2;
+  const int threads = hidden >= 512 ? 256 : 128;
+  if (dtype == RL_F32)
+    rl::launch_pdl(rl::embed_pair_kernel<float>, n_tokens, threads, 0, stream, ids, pos, req_of_token, q_start, slots,
+                   (const float*)table, (const float*)pos_table, (const float*)pair_table, out, n_tokens, hidden, vocab,
+                   n_positions, buckets, mul_prev, mul_cur, last_token, status, feedback, n_feedback);
+  else
+    rl::launch_pdl(rl::embed_pair_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, ids, pos, req_of_token, q_start,
+                   slots, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table,
+                   (const __nv_bfloat16*)pair_table, out, n_tokens, hidden, vocab, n_positions, buckets, mul_prev,
+                   mul_cur, last_token, status, feedback, n_feedback);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+namespace rl {
+
 // The same for few rows (a decode step of a wide model, a norm before 17 to 64 rows' products):
 // a block per row, so that a row's latency is not one warp's walk through it: every thread holds
 // two 16-byte pieces (one, where the row is short), the statistics meet through shared memory, and gamma and beta (no

@@ -1,7 +1,7 @@
 // Mixture of experts: routing, and the experts' gated feed-forward as grouped products.
 //
 // Routing (`moe_select_kernel`, one warp per token, float32): scores s = softmax(z) over all
-// experts; the choice is made on s + correction, the weights are the chosen experts' s.  With
+// experts, or (score_kind 1) s = sigmoid(z) of each expert by itself; the choice is made on s + correction, the weights are the chosen experts' s.  With
 // groups, the experts form `group_count` equal groups of neighbours, a group's score is the
 // largest choice score in it, and only experts of the best `group_keep` groups can be chosen
 // (the others count as minus infinity).  Ties go to the lower index.
@@ -12,7 +12,10 @@
 // on its token count alone.  `moe_ffn1_kernel` computes a tile of f(h W_gate^T, h W_up^T) with
 // the rows of h gathered by token, `moe_ffn2_kernel` the tile's product with W_down, and
 // `moe_combine_kernel` sums a token's expert outputs in the order of its choices, times their
-// weights (a fixed order: the result does not depend on where the pairs were placed).
+// weights (a fixed order: the result does not depend on where the pairs were placed).  Where the
+// weight belongs on the expert's INPUT instead (expert(w * h)), `moe_scatter_kernel` leaves each
+// place's weight in `place_weight`, the first product scales its two results by it before the
+// gate function (W (w h) = w (W h)), and the sum at the end takes no weights.
 // Products: float32 as IEEE multiply-adds on 64 x 64 tiles (tile_gemm.cuh); bfloat16 on the tensor
 // cores (mma_tile.cuh) with float32 accumulation, or, where an expert has a few rows only (decode
 // steps), by `moe_rows_kernel`, which streams the weights once with a warp an output column.
@@ -45,7 +48,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 __global__ __launch_bounds__(128) void moe_select_kernel(const float* __restrict__ z, long ldz,
                                                          const float* __restrict__ correction, int n_tokens,
                                                          int n_experts, int top, int group_count, int group_keep,
-                                                         int* __restrict__ ids, float* __restrict__ weights,
+                                                         int score_kind, int* __restrict__ ids, float* __restrict__ weights,
                                                          int* __restrict__ counts) {
   extern __shared__ float smem[];
   pdl_begin();
@@ -57,18 +60,23 @@ __global__ __launch_bounds__(128) void moe_select_kernel(const float* __restrict
   float* c_w = s_w + E;                      // choice scores
   float* g_w = c_w + E;                      // group scores
   const float* zr = z + (size_t)t * ldz;
-  float mx = -CUDART_INF_F;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float ex = expf(zr[e] - mx);
-    s_w[e] = ex;
-    sum += ex;
+  float sum = 1.f;
+  if (score_kind == 1) {
+    for (int e = lane; e < E; e += 32) s_w[e] = 1.0f / (1.0f + expf(-zr[e]));
+  } else {
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+    mx = warp_max(mx);
+    sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float ex = expf(zr[e] - mx);
+      s_w[e] = ex;
+      sum += ex;
+    }
+    sum = warp_sum(sum);
   }
-  sum = warp_sum(sum);
   for (int e = lane; e < E; e += 32) {
-    const float s = s_w[e] / sum;
+    const float s = score_kind == 1 ? s_w[e] : s_w[e] / sum;
     s_w[e] = s;
     c_w[e] = s + (correction != nullptr ? correction[e] : 0.f);
   }
@@ -162,7 +170,8 @@ __global__ __launch_bounds__(256) void moe_plan_kernel(int* __restrict__ counts,
 
 __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ offsets,
                                    int* __restrict__ fill, int* __restrict__ row_token, int* __restrict__ place_of,
-                                   int n_pairs, int top) {
+                                   const float* __restrict__ weights, float* __restrict__ place_weight, int n_pairs,
+                                   int top) {
   pdl_begin();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
@@ -170,13 +179,15 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
   const int place = offsets[e] + atomicAdd(&fill[e], 1);
   row_token[place] = i / top;
   place_of[i] = place;
+  if (place_weight != nullptr) place_weight[place] = weights[i];
 }
 
 // act[place, f] = f(h[token] . W_gate[e, f], h[token] . W_up[e, f]).  w_gu: [experts][2][ff][hidden].
 template <typename T>
 __global__ __launch_bounds__(256) void moe_ffn1_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ w_gu,
                                                        const int* __restrict__ tiles, const int* __restrict__ meta,
-                                                       const int* __restrict__ row_token, T* __restrict__ act,
+                                                       const int* __restrict__ row_token,
+                                                       const float* __restrict__ row_scale, T* __restrict__ act,
                                                        long lda, int hidden, int ff, int kind, float alpha,
                                                        float limit) {
   __shared__ TileGemmSmem s;
@@ -202,10 +213,12 @@ __global__ __launch_bounds__(256) void moe_ffn1_kernel(const T* __restrict__ h, 
   for (int i = 0; i < 4; ++i) {
     const int m = ty * 4 + i;
     if (m >= rows) continue;
+    const float sc = row_scale != nullptr ? row_scale[row0 + m] : 1.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < ff) act[(size_t)(row0 + m) * lda + n] = from_f32<T>(gated_value(acc_g[i][j], acc_u[i][j], kind, alpha, limit));
+      if (n < ff)
+        act[(size_t)(row0 + m) * lda + n] = from_f32<T>(gated_value(sc * acc_g[i][j], sc * acc_u[i][j], kind, alpha, limit));
     }
   }
 }
@@ -245,6 +258,7 @@ __global__ __launch_bounds__(128) void moe_ffn1_mma_kernel(const __nv_bfloat16* 
                                                            const __nv_bfloat16* __restrict__ w_gu,
                                                            const int* __restrict__ tiles, const int* __restrict__ meta,
                                                            const int* __restrict__ row_token,
+                                                           const float* __restrict__ row_scale,
                                                            __nv_bfloat16* __restrict__ act, long lda, int hidden, int ff,
                                                            int kind, float alpha, float limit) {
   __shared__ __align__(16) MmaTileSmem s;
@@ -264,9 +278,11 @@ __global__ __launch_bounds__(128) void moe_ffn1_mma_kernel(const __nv_bfloat16* 
       [&](int n) { return n0 + n < ff ? wg + (size_t)(n0 + n) * hidden : nullptr; },
       [&](int n) { return n0 + n < ff ? wu + (size_t)(n0 + n) * hidden : nullptr; }, s, up_s);
   mma_for_each(acc_g, [&](int m, int n, int mi, int ni, int c) {
-    if (m < rows && n0 + n < ff)
+    if (m < rows && n0 + n < ff) {
+      const float sc = row_scale != nullptr ? row_scale[row0 + m] : 1.f;
       act[(size_t)(row0 + m) * lda + n0 + n] =
-          __float2bfloat16_rn(gated_value(acc_g[mi][ni][c], acc_u[mi][ni][c], kind, alpha, limit));
+          __float2bfloat16_rn(gated_value(sc * acc_g[mi][ni][c], sc * acc_u[mi][ni][c], kind, alpha, limit));
+    }
   });
 }
 
@@ -302,6 +318,7 @@ __global__ __launch_bounds__(256) void moe_rows_kernel(const __nv_bfloat16* __re
                                                        const __nv_bfloat16* __restrict__ w,
                                                        const int* __restrict__ tiles, const int* __restrict__ meta,
                                                        const int* __restrict__ row_token,
+                                                       const float* __restrict__ row_scale,
                                                        __nv_bfloat16* __restrict__ act, long lda,
                                                        float* __restrict__ eo, int k_total, int n_total, int kind,
                                                        float alpha, float limit) {
@@ -351,16 +368,17 @@ __global__ __launch_bounds__(256) void moe_rows_kernel(const __nv_bfloat16* __re
       const float s0 = warp_sum(a0[r]);
       const float s1 = PAIR ? warp_sum(a1[r]) : 0.f;
       if (lane == 0 && n < n_total) {
-        if (PAIR)
-          act[(size_t)(row0 + r0 + r) * lda + n] = __float2bfloat16_rn(gated_value(s0, s1, kind, alpha, limit));
-        else
+        if (PAIR) {
+          const float sc = row_scale != nullptr ? row_scale[row0 + r0 + r] : 1.f;
+          act[(size_t)(row0 + r0 + r) * lda + n] = __float2bfloat16_rn(gated_value(sc * s0, sc * s1, kind, alpha, limit));
+        } else
           eo[(size_t)(row0 + r0 + r) * n_total + n] = s0;
       }
     }
   }
 }
 
-// y[t] (+)= sum_j weights[t, j] * eo[place_of[t, j]], j in order.
+// y[t] (+)= sum_j weights[t, j] * eo[place_of[t, j]], j in order (weights null: plain sum).
 __global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restrict__ eo,
                                                           const float* __restrict__ weights,
                                                           const int* __restrict__ place_of, float* __restrict__ y,
@@ -371,7 +389,8 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restric
   for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j)
-      acc = fmaf(weights[(size_t)t * top + j], eo[(size_t)place_of[(size_t)t * top + j] * hidden + d], acc);
+      acc = fmaf(weights != nullptr ? weights[(size_t)t * top + j] : 1.f,
+                 eo[(size_t)place_of[(size_t)t * top + j] * hidden + d], acc);
     float* o = y + (size_t)t * ldy + d;
     *o = add ? *o + acc : acc;
   }
@@ -382,10 +401,10 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(const float* __restric
 // z: float32 router logits [tokens, experts] (row stride ldz).  ids, weights: [tokens * top].
 // counts: [experts], zero on entry; holds the experts' pair counts afterwards.
 RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, int n_tokens, int n_experts, int top,
-                            int group_count, int group_keep, int* ids, float* weights, int* counts,
+                            int group_count, int group_keep, int score_kind, int* ids, float* weights, int* counts,
                             cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (n_experts <= 0 || n_experts > 2048 || top <= 0 || top > n_experts) return -2;
+  if (n_experts <= 0 || n_experts > 2048 || top <= 0 || top > n_experts || score_kind < 0 || score_kind > 1) return -2;
   if (group_count < 1 || n_experts % group_count != 0 || group_keep < 1 || group_keep > group_count ||
       top > group_keep * (n_experts / group_count))
     return -3;
@@ -393,7 +412,7 @@ RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, i
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(rl::moe_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   rl::launch_pdl(rl::moe_select_kernel, (n_tokens + 3) / 4, 128, smem, stream, z, ldz, correction, n_tokens, n_experts,
-                 top, group_count, group_keep, ids, weights, counts);
+                 top, group_count, group_keep, score_kind, ids, weights, counts);
   RL_CHECK_LAUNCH();
   return 0;
 }
@@ -401,15 +420,17 @@ RL_EXPORT int rl_moe_select(const float* z, long ldz, const float* correction, i
 // The pairs laid out expert by expert: offsets [experts + 1], tiles [max_tiles][3], meta [1],
 // row_token and place_of [tokens * top].  counts as rl_moe_select left it, zero afterwards;
 // fill is scratch.  max_tiles >= rl_moe_max_tiles(pairs, experts).
+// weights, place_weight: both null, or the pairs' weights and a float32 [tokens * top] that receives them by place.
 RL_EXPORT int rl_moe_plan(const int* ids, int* counts, int* fill, int* offsets, int* tiles, int* meta, int* row_token,
-                          int* place_of, int n_tokens, int n_experts, int top, cudaStream_t stream) {
+                          int* place_of, const float* weights, float* place_weight, int n_tokens, int n_experts, int top,
+                          cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (n_experts <= 0 || n_experts > 2048) return -2;
   rl::launch_pdl(rl::moe_plan_kernel, 1, 256, (size_t)2 * (n_experts + 1) * sizeof(int), stream, counts, fill, offsets,
                  tiles, meta, n_experts);
   const int pairs = n_tokens * top;
   rl::launch_pdl(rl::moe_scatter_kernel, (pairs + 255) / 256, 256, 0, stream, ids, (const int*)offsets, fill, row_token,
-                 place_of, pairs, top);
+                 place_of, weights, place_weight, pairs, top);
   RL_CHECK_LAUNCH();
   return 0;
 }
@@ -422,9 +443,10 @@ RL_EXPORT int rl_moe_max_tiles(int n_pairs, int n_experts) {
 // h: [tokens, hidden] (row stride ldh); w_gu: [experts][2][ff][hidden]; w_down:
 // [experts][hidden][ff]; act: scratch [pairs, ff] (row stride lda); eo: float32 scratch
 // [pairs, hidden]; y: float32 [tokens, hidden] (row stride ldy), overwritten or (add) added to.
+// place_weight (by place) scales the experts' inputs, weights (by pair) their outputs; either may be null.
 RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_gu, const void* w_down, const int* tiles,
                              const int* meta, const int* row_token, const int* place_of, const float* weights,
-                             void* act, long lda, float* eo, float* y, long ldy, int n_tokens, int hidden, int ff,
+                             const float* place_weight, void* act, long lda, float* eo, float* y, long ldy, int n_tokens, int hidden, int ff,
                              int n_experts, int top, int kind, float alpha, float limit, int add,
                              cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
@@ -434,7 +456,7 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
   if (g1.y > 65535 || g2.y > 65535) return -2;
   if (dtype == RL_F32) {
     rl::launch_pdl(rl::moe_ffn1_kernel<float>, g1, 256, 0, stream, (const float*)h, ldh, (const float*)w_gu, tiles,
-                   meta, row_token, (float*)act, lda, hidden, ff, kind, alpha, limit);
+                   meta, row_token, place_weight, (float*)act, lda, hidden, ff, kind, alpha, limit);
     rl::launch_pdl(rl::moe_ffn2_kernel<float>, g2, 256, 0, stream, (const float*)act, lda, (const float*)w_down, tiles,
                    meta, eo, hidden, ff);
   } else {
@@ -448,11 +470,11 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
     if (few) {
       rl::launch_pdl(rl::moe_rows_kernel<true>, dim3(max_tiles, (ff + 7) / 8), 256,
                      (size_t)rl::MOE_ROWS_PASS * hidden * 2, stream, (const __nv_bfloat16*)h, ldh,
-                     (const __nv_bfloat16*)w_gu, tiles, meta, row_token, (__nv_bfloat16*)act, lda, (float*)nullptr,
+                     (const __nv_bfloat16*)w_gu, tiles, meta, row_token, place_weight, (__nv_bfloat16*)act, lda, (float*)nullptr,
                      hidden, ff, kind, alpha, limit);
       rl::launch_pdl(rl::moe_rows_kernel<false>, dim3(max_tiles, (hidden + 7) / 8), 256,
                      (size_t)rl::MOE_ROWS_PASS * ff * 2, stream, (const __nv_bfloat16*)act, lda,
-                     (const __nv_bfloat16*)w_down, tiles, meta, row_token, (__nv_bfloat16*)nullptr, 0L, eo, ff, hidden,
+                     (const __nv_bfloat16*)w_down, tiles, meta, row_token, (const float*)nullptr, (__nv_bfloat16*)nullptr, 0L, eo, ff, hidden,
                      kind, alpha, limit);
     } else {
     auto k1 = vec1 ? rl::moe_ffn1_mma_kernel<true> : rl::moe_ffn1_mma_kernel<false>;
@@ -469,7 +491,7 @@ RL_EXPORT int rl_moe_experts(int dtype, const void* h, long ldh, const void* w_g
       carved[2 + vec2] = true;
     }
     rl::launch_pdl_split(false, k1, g1, 128, 0, stream, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gu, tiles,
-                         meta, row_token, (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
+                         meta, row_token, place_weight, (__nv_bfloat16*)act, lda, hidden, ff, kind, alpha, limit);
     rl::launch_pdl_split(false, k2, g2, 128, 0, stream, (const __nv_bfloat16*)act, lda, (const __nv_bfloat16*)w_down,
                          tiles, meta, eo, hidden, ff);
     }

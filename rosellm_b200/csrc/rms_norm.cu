@@ -86,6 +86,42 @@ __global__ __launch_bounds__(256) void rmsnorm_add_kernel(const float* __restric
   }
 }
 
+// stream[i] += rmsnorm(y[i]) * gamma, and next[i] = rmsnorm(stream[i]) * gamma_next of the new row, in one
+// pass: the norm after one sublayer and the norm before the next (a layer that normalises its sublayers on
+// both sides).  The row is kept in shared memory between the two statistics.
+template <typename TOut>
+__global__ __launch_bounds__(256) void rmsnorm_add_norm_kernel(const float* __restrict__ y, long ldy,
+                                                               const float* __restrict__ gamma,
+                                                               float* __restrict__ stream, long lds,
+                                                               const float* __restrict__ gamma_next,
+                                                               TOut* __restrict__ next, long ldn, int n_rows, int width,
+                                                               float eps, float eps_next) {
+  extern __shared__ float row_s[];  // [width] + 33
+  float* scratch = row_s + width;
+  pdl_begin();
+  const int i = blockIdx.x;
+  if (i >= n_rows) return;
+  const float* yr = y + (size_t)i * ldy;
+  float* xr = stream + (size_t)i * lds;
+  float s = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = yr[d];
+    row_s[d] = v;
+    s = fmaf(v, v, s);
+  }
+  const float r = 1.0f / sqrtf(block_sum(s, scratch) / (float)width + eps);
+  float s2 = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float v = xr[d] + row_s[d] * r * gamma[d];
+    xr[d] = v;
+    row_s[d] = v;
+    s2 = fmaf(v, v, s2);
+  }
+  const float r2 = 1.0f / sqrtf(block_sum(s2, scratch) / (float)width + eps_next);
+  TOut* o = next + (size_t)i * ldn;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = from_f32<TOut>(row_s[d] * r2 * gamma_next[d]);
+}
+
 __global__ void cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long n) {
   pdl_begin();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -133,6 +169,23 @@ RL_EXPORT int rl_rmsnorm_add(const float* y, long ldy, const float* gamma, float
 RL_EXPORT int rl_cast_rows(const float* x, void* out, long n, cudaStream_t stream) {
   if (n <= 0) return 0;
   rl::launch_pdl(rl::cast_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, (__nv_bfloat16*)out, n);
+  RL_CHECK_LAUNCH();
+  return 0;
+}
+
+// stream += rmsnorm(y) * gamma; next = rmsnorm(new stream rows) * gamma_next (out_dtype: RL_F32 or RL_BF16).
+RL_EXPORT int rl_rmsnorm_add_norm(int out_dtype, const float* y, long ldy, const float* gamma, float* stream_rows,
+                                  long lds, const float* gamma_next, void* next, long ldn, int n_rows, int width,
+                                  float eps, float eps_next, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (width <= 0 || width > 48 * 1024 / 4 - 64) return -2;
+  const size_t smem = (size_t)(width + 33) * sizeof(float);
+  if (out_dtype == RL_F32)
+    rl::launch_pdl(rl::rmsnorm_add_norm_kernel<float>, n_rows, rl::norm_threads(width), smem, stream, y, ldy, gamma,
+                   stream_rows, lds, gamma_next, (float*)next, ldn, n_rows, width, eps, eps_next);
+  else
+    rl::launch_pdl(rl::rmsnorm_add_norm_kernel<__nv_bfloat16>, n_rows, rl::norm_threads(width), smem, stream, y, ldy,
+                   gamma, stream_rows, lds, gamma_next, (__nv_bfloat16*)next, ldn, n_rows, width, eps, eps_next);
   RL_CHECK_LAUNCH();
   return 0;
 }

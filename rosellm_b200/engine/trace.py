@@ -33,7 +33,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="tokens the live requests hold at most, each rounded up to a multiple of 64")
     p.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
-    p.add_argument("--max-requests", type=int, default=8, help="requests live at once")
+    p.add_argument("--max-requests", type=int, default=4, help="requests live at once (state slots)")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--cuda-graphs", action="store_true",
                    help="replay steps in which every request brings one token and wants its logits from "

@@ -1,5 +1,6 @@
 from . import gpt2  # registers GPT2LMHeadModel
 from . import lebedra  # registers Lebedra
+from . import porovik  # registers Porovik
 from .model import Layer, Model, named_params_of_spec
 
-__all__ = ["Layer", "Model", "named_params_of_spec", "gpt2", "lebedra"]
+__all__ = ["Layer", "Model", "named_params_of_spec", "gpt2", "lebedra", "porovik"]

@@ -133,7 +133,12 @@ class Model:
         return out
 
     def state_specs(self) -> dict:
+        """``StateSpec`` of every part that keeps per-request state: a layer's sub-parts by their cache
+        key, the embedding (the last token of a request, say) under ``"embedding"``."""
         out = {}
+        ss = self.embedding.state_spec()
+        if ss is not None:
+            out["embedding"] = ss
         for i, layer in enumerate(self.layers):
             for name, part in layer.parts.items():
                 ss = part.state_spec()

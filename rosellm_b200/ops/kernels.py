@@ -94,7 +94,7 @@ class _RecordingLib:
 
 _QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster",
             "rl_host_memory_on_device", "rl_latent_attention_fits", "rl_latent_decode_fits",
-            "rl_moe_max_tiles")  # library functions that launch nothing
+            "rl_moe_max_tiles", "rl_bias_attention_shape")  # library functions that launch nothing
 
 
 class recording:
@@ -163,13 +163,22 @@ def _lib() -> ctypes.CDLL:
         lib.rl_head_linear.argtypes = [I, P, L, L, P, L, L, L, P, L, L, I, I, I, I, P]
         lib.rl_gated_act.argtypes = [I, P, L, I, P, L, I, I, I, F, F, P]
         lib.rl_token_gate.argtypes = [I, P, L, P, P, L, I, I, P, L, I, I, I, P, I, P, P]
-        lib.rl_moe_select.argtypes = [P, L, P, I, I, I, I, I, P, P, P, P]
-        lib.rl_moe_plan.argtypes = [P, P, P, P, P, P, P, P, I, I, I, P]
+        lib.rl_moe_select.argtypes = [P, L, P, I, I, I, I, I, I, P, P, P, P]
+        lib.rl_moe_plan.argtypes = [P, P, P, P, P, P, P, P, P, P, I, I, I, P]
         lib.rl_moe_max_tiles.argtypes = [I, I]
-        lib.rl_moe_experts.argtypes = [I, P, L, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, F, F, I, P]
+        lib.rl_moe_experts.argtypes = [I, P, L, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, F, F, I, P]
+        lib.rl_embed_pair.argtypes = [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P]
+        lib.rl_rmsnorm_add_norm.argtypes = [I, P, L, P, P, L, P, P, L, I, I, F, F, P]
+        lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, I, I, I, I, F, F, F, P]
+        lib.rl_bias_attention_shape.argtypes = [I, P, P]
+        lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
+                                          F, F, I, P, P, P]
+        lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
-                     "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts"):
+                     "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts", "rl_embed_pair",
+                     "rl_rmsnorm_add_norm", "rl_recurrence", "rl_bias_attention_shape", "rl_bias_attention",
+                     "rl_bias_kv_store"):
             getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
                      "rl_gemm_rows_smem", "rl_gemm_rows_smem_fits",
@@ -1106,9 +1115,14 @@ def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
     return int(_lib().rl_moe_max_tiles(n_pairs, n_experts))
 
 
-def moe_select(z, correction, *, top: int, group_count: int, group_keep: int, ids, weights, counts) -> None:
+MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_select(z, correction, *, top: int, group_count: int, group_keep: int, ids, weights, counts,
+               score: int = 0) -> None:
     """Routing of every row of the float32 router logits ``z`` [tokens, experts]: see csrc/moe.cu.
-    ``ids`` int32 and ``weights`` float32 [tokens * top]; ``counts`` int32 [experts], zero on entry."""
+    ``ids`` int32 and ``weights`` float32 [tokens * top]; ``counts`` int32 [experts], zero on entry.
+    ``score``: 0 softmax over the experts, 1 each expert's sigmoid."""
     _need(z, "z", torch.float32, contiguous=False)
     n, n_experts = z.shape
     for t, name, dt in ((ids, "ids", torch.int32), (weights, "weights", torch.float32), (counts, "counts", torch.int32)):
@@ -1116,25 +1130,31 @@ def moe_select(z, correction, *, top: int, group_count: int, group_keep: int, id
     if correction is not None:
         _need(correction, "correction", torch.float32)
     rc = _lib().rl_moe_select(_ptr(z), z.stride(0), _ptr(correction), n, n_experts, top, group_count, group_keep,
-                              _ptr(ids), _ptr(weights), _ptr(counts), _stream())
+                              int(score), _ptr(ids), _ptr(weights), _ptr(counts), _stream())
     if rc in (-2, -3):
         raise KernelError(f"moe_select: {n_experts} experts, top {top}, {group_keep} of {group_count} groups not taken")
     _ok(rc, "moe_select")
 
 
-def moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, *, n_tokens: int, n_experts: int, top: int) -> None:
-    """Lay the chosen pairs out expert by expert (all int32 device buffers; see csrc/moe.cu)."""
+def moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, *, n_tokens: int, n_experts: int, top: int,
+             weights=None, place_weight=None) -> None:
+    """Lay the chosen pairs out expert by expert (all int32 device buffers; see csrc/moe.cu).
+    With ``weights`` and ``place_weight`` (float32 [tokens * top]) the pairs' weights are left by
+    place, for experts whose INPUT is weighted."""
+    if (weights is None) != (place_weight is None):
+        raise KernelError("moe_plan: weights and place_weight go together")
     rc = _lib().rl_moe_plan(_ptr(ids), _ptr(counts), _ptr(fill), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(row_token),
-                            _ptr(place_of), n_tokens, n_experts, top, _stream())
+                            _ptr(place_of), _ptr(weights), _ptr(place_weight), n_tokens, n_experts, top, _stream())
     _ok(rc, "moe_plan")
     global _launches
     _launches += 1
 
 
 def moe_experts(h, w_gate_up, w_down, tiles, meta, row_token, place_of, weights, act, eo, y, *, n_experts: int, top: int,
-                ff: int, gate: int, alpha: float, limit: float, add: bool) -> None:
+                ff: int, gate: int, alpha: float, limit: float, add: bool, place_weight=None) -> None:
     """The experts' gated feed-forward on the laid-out pairs and the weighted sum per token into
-    ``y`` float32 [tokens, hidden] (``add``: added to it).  ``w_gate_up`` [experts * 2 * ff, hidden]
+    ``y`` float32 [tokens, hidden] (``add``: added to it).  ``weights`` (by pair) weight the experts'
+    outputs; ``place_weight`` (by place, from ``moe_plan``) their inputs instead; either may be ``None``.  ``w_gate_up`` [experts * 2 * ff, hidden]
     (per expert: gate rows, then up rows), ``w_down`` [experts * hidden, ff]."""
     _need(h, "h", contiguous=False)
     _need(w_gate_up, "w_gate_up", h.dtype)
@@ -1147,9 +1167,167 @@ def moe_experts(h, w_gate_up, w_down, tiles, meta, row_token, place_of, weights,
             or act.shape[0] < n * top or act.shape[1] < ff or eo.numel() < n * top * hidden or tuple(y.shape) != (n, hidden):
         raise KernelError("moe_experts: shapes do not fit")
     rc = _lib().rl_moe_experts(_code(h), _ptr(h), h.stride(0), _ptr(w_gate_up), _ptr(w_down), _ptr(tiles), _ptr(meta),
-                               _ptr(row_token), _ptr(place_of), _ptr(weights), _ptr(act), act.stride(0), _ptr(eo), _ptr(y),
+                               _ptr(row_token), _ptr(place_of), _ptr(weights), _ptr(place_weight), _ptr(act), act.stride(0), _ptr(eo), _ptr(y),
                                y.stride(0), n, hidden, ff, n_experts, top, gate, float(alpha), float(limit), int(add),
                                _stream())
     _ok(rc, "moe_experts")
     global _launches
     _launches += 2
+
+
+# ---- embedding with a table chosen by pairs of tokens ------------------------------------------
+
+def embed_pair(token_ids, positions, req_of_token, q_start, slots, table, pos_table, pair_table, out, last_token, *,
+               buckets: int, mul_prev: int, mul_cur: int, feedback=None) -> None:
+    """out[n] = table[id_n] + pair_table[(prev_n * mul_prev + id_n * mul_cur) mod buckets] (+ pos_table[pos_n]);
+    a sequence's first token takes row ``buckets`` of ``pair_table``.  ``last_token`` int32 [slots, 1]:
+    each request's last token so far (read for a portion's first token, then brought up to date)."""
+    _need(token_ids, "token_ids", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(table, "table")
+    _need(pair_table, "pair_table", table.dtype)
+    _need(out, "out", torch.float32)
+    _need(last_token, "last_token", torch.int32)
+    n, hidden = out.shape
+    if table.shape[1] != hidden or pair_table.shape[1] != hidden or pair_table.shape[0] != buckets + 1:
+        raise KernelError("embed_pair: table widths differ from out, or the pair table has not buckets + 1 rows")
+    n_pos = 0
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype)
+        n_pos = pos_table.shape[0]
+    rc = _lib().rl_embed_pair(_code(table), _ptr(token_ids), _ptr(positions), _ptr(req_of_token), _ptr(q_start),
+                              _ptr(slots), _ptr(table), _ptr(pos_table), _ptr(pair_table), _ptr(out), n, hidden,
+                              table.shape[0], n_pos, int(buckets), int(mul_prev), int(mul_cur), _ptr(last_token),
+                              _ptr(status_word(out.device)), _ptr(feedback), 0 if feedback is None else feedback.numel(),
+                              _stream())
+    _ok(rc, "embed_pair")
+
+
+def rmsnorm_add_norm(y, gamma, eps: float, stream_rows, gamma_next, eps_next: float, out_next) -> None:
+    """stream_rows += y / sqrt(mean(y^2) + eps) * gamma, then out_next = the new rows normalised with
+    ``gamma_next`` (float32 or bfloat16): the norm behind one sublayer and the norm ahead of the next in one pass."""
+    _need(y, "y", torch.float32, contiguous=False)
+    _need(gamma, "gamma", torch.float32)
+    _need(gamma_next, "gamma_next", torch.float32)
+    _need(stream_rows, "stream_rows", torch.float32, contiguous=False)
+    _need(out_next, "out_next", contiguous=False)
+    n, width = stream_rows.shape
+    if tuple(y.shape) != (n, width) or tuple(out_next.shape) != (n, width) or gamma.numel() != width \
+            or gamma_next.numel() != width or y.stride(1) != 1 or stream_rows.stride(1) != 1 or out_next.stride(1) != 1:
+        raise KernelError("rmsnorm_add_norm: shapes differ")
+    rc = _lib().rl_rmsnorm_add_norm(_code(out_next), _ptr(y), y.stride(0), _ptr(gamma), _ptr(stream_rows),
+                                    stream_rows.stride(0), _ptr(gamma_next), _ptr(out_next), out_next.stride(0), n, width,
+                                    float(eps), float(eps_next), _stream())
+    if rc == -2:
+        raise KernelError(f"rmsnorm_add_norm: rows of {width} elements do not fit a block's shared memory")
+    _ok(rc, "rmsnorm_add_norm")
+
+
+RMSNORM_ADD_NORM_MAX_WIDTH = 48 * 1024 // 4 - 64
+
+
+# ---- mixers with a matrix-valued state -------------------------------------------------------------
+
+RECURRENCES = {"delta": 0, "gated": 1}
+
+
+def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, *, n_reqs: int, n_heads: int, dk: int,
+               dv: int, eps: float, a_bias, w0, out_weight, w2=None, rank: int = 0, decay_scale: float = 0.0,
+               unit_eps: float = 0.0) -> None:
+    """One step of a recurrence over matrix states (csrc/recurrent.cu) for every request of the step.
+    ``proj`` float32 [tokens, columns]: the packed projections, ``offsets`` the first column of
+    ``r``, ``k``, ``v``, ``a``, ``g``, ``w`` (those the form has); ``state`` float32
+    [slots, heads, dk, dv]; ``out`` [tokens, heads * dv] float32 or bfloat16."""
+    _need(proj, "proj", torch.float32, contiguous=False)
+    _need(state, "state", torch.float32)
+    _need(out, "out", contiguous=False)
+    for t, name in ((a_bias, "a_bias"), (w0, "w0"), (out_weight, "out_weight")):
+        _need(t, name, torch.float32)
+    if w2 is not None:
+        _need(w2, "w2", torch.float32)
+        if tuple(w2.shape) != (n_heads * dk, rank):
+            raise KernelError("recurrence: the low-rank matrix has another shape")
+    if tuple(state.shape[1:]) != (n_heads, dk, dv) or out.shape[1] != n_heads * dv or proj.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("recurrence: shapes do not fit")
+    if mode == 0 and (w2 is None or rank <= 0):
+        raise KernelError("recurrence: the delta form needs its low-rank decay")
+    off = [int(offsets.get(k, -1)) for k in ("r", "k", "v", "a", "g", "w")]
+    rc = _lib().rl_recurrence(int(mode), _code(out), _ptr(proj), proj.stride(0), *off, _ptr(a_bias), _ptr(w0), _ptr(w2),
+                              int(rank), _ptr(out_weight), _ptr(state), _ptr(out), out.stride(0), _ptr(q_start),
+                              _ptr(slots), n_reqs, n_heads, dk, dv, float(eps), float(decay_scale), float(unit_eps),
+                              _stream())
+    if rc == -2:
+        raise KernelError(f"recurrence: sizes not taken (key size {dk}, value size {dv}: up to 256 each)")
+    _ok(rc, "recurrence")
+
+
+# ---- attention with a distance bias over rows of [key | value] -------------------------------------
+
+def bias_attention_shape(heads_per_group: int) -> tuple[int, int]:
+    """(heads a block, tokens a block) of ``bias_attention`` for so many query heads a key/value head."""
+    hb, tt = c_int(0), c_int(0)
+    if _lib().rl_bias_attention_shape(int(heads_per_group), ctypes.byref(hb), ctypes.byref(tt)) != 0:
+        raise KernelError("bias_attention_shape: heads per group must be positive")
+    return hb.value, tt.value
+
+
+def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_at: int, max_pos: int, mix: int = 0,
+                  v_src=None, lam=None) -> None:
+    """The step's keys ``k`` [tokens, kv heads * dk] and values ``v`` [tokens, kv heads * dv] (float32 views)
+    into the pool [pages, 1, kv heads, page, row], the value at entry ``v_at`` of a row.  ``mix`` 1: the
+    values are also left in ``v_src`` (float32 [tokens, kv heads * dv]); 2: v <- (1 - lam) v + lam v_src
+    (``lam`` a float32 device scalar) is what is cached."""
+    _need(k, "k", torch.float32, contiguous=False)
+    _need(v, "v", torch.float32, contiguous=False)
+    _need(pool, "pool")
+    n = k.shape[0]
+    _, planes, n_kv, page_size, row = pool.shape
+    dk, dv = k.shape[1] // n_kv, v.shape[1] // n_kv
+    if planes != 1 or k.shape[1] != n_kv * dk or v.shape[1] != n_kv * dv or v.shape[0] != n:
+        raise KernelError("bias_kv_store: shapes do not fit the pool")
+    if v_src is not None:
+        _need(v_src, "v_src", torch.float32)
+        if v_src.numel() < n * n_kv * dv:
+            raise KernelError("bias_kv_store: the value source is too small")
+    if lam is not None:
+        _need(lam, "lam", torch.float32)
+    rc = _lib().rl_bias_kv_store(_code(pool), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(v_src), _ptr(lam), int(mix),
+                                 _ptr(pool), _ptr(block_table), block_table.stride(0), _ptr(positions), _ptr(req_of_token),
+                                 _ptr(slots), n, n_kv, dk, dv, int(v_at), row, page_size,
+                                 min(block_table.shape[1], -(-max_pos // page_size)), _ptr(status_word(pool.device)),
+                                 _stream())
+    if rc == -2:
+        raise KernelError("bias_kv_store: the mixing mode lacks its buffers, or the value does not fit the row")
+    _ok(rc, "bias_kv_store")
+
+
+def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, dk: int, dv: int, v_at: int,
+                   scale: float, slopes=None, temp_coef: float = 0.0, temp_every: int = 0, tiles=None, n_tiles: int = 0,
+                   tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int) -> None:
+    """Causal attention of the step's queries over the cached rows (csrc/bias_attention.cu).
+    ``q`` float32 [tokens, heads * dk] and ``gate`` float32 [tokens, heads * dv] (or ``None``) may be views
+    with a row stride; ``out`` [tokens, heads * dv] float32 or bfloat16; ``slopes`` float32 [heads] or ``None``."""
+    _need(q, "q", torch.float32, contiguous=False)
+    _need(out, "out", contiguous=False)
+    _need(pool, "pool")
+    _, planes, n_kv, page_size, row = pool.shape
+    if planes != 1 or q.shape[1] != n_heads * dk or out.shape[1] != n_heads * dv or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("bias_attention: shapes do not fit")
+    if gate is not None:
+        _need(gate, "gate", torch.float32, contiguous=False)
+        if gate.shape[1] != n_heads * dv or gate.stride(1) != 1:
+            raise KernelError("bias_attention: the gate has another shape")
+    if slopes is not None:
+        _need(slopes, "slopes", torch.float32)
+        if slopes.numel() != n_heads:
+            raise KernelError("bias_attention: one slope a head")
+    rc = _lib().rl_bias_attention(_code(pool), _code(out), _ptr(q), q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
+                                  _ptr(pool), _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len),
+                                  _ptr(slots), _ptr(tiles), int(n_tiles), int(tile_tokens), _ptr(decode_reqs), int(n_decode),
+                                  _ptr(out), out.stride(0), n_heads, n_kv, dk, dv, int(v_at), row, page_size,
+                                  min(block_table.shape[1], -(-max_pos // page_size)), float(scale), float(temp_coef),
+                                  int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), _stream())
+    if rc in (-2, -3):
+        raise KernelError(f"bias_attention: sizes not taken (code {rc}: key and value sizes up to 256; tiles a multiple "
+                          "of the tokens a block takes)")
+    _ok(rc, "bias_attention")

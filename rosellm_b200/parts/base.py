@@ -68,7 +68,9 @@ class ParamSpec:
     """One tensor a part reads.
 
     ``role`` is the part's own name for it; the ``PartSpec.tensors`` map gives
-    its name in the weight file.  ``shape`` is the shape in the file.
+    its name in the weight file.  ``shape`` is the shape in the file; an extent of -1 there is
+    whatever the file has (a low rank that no configuration key gives: the part reads it off the
+    tensor when it is bound; the random-weights mode needs it given).
     ``kind`` decides how it is kept on the device:
     ``matrix``: the engine's compute dtype (bfloat16 or float32);
     ``vector``: float32 in both modes (norm scales, biases: small, and read

@@ -66,10 +66,11 @@ class MixtureOfExperts(Part):
     """``num_experts`` gated feed-forward layers of which a token uses ``top``.
 
     Router logits ``z = W_router h`` with float32 accumulation and output; scores
-    ``s = softmax(z)`` over all experts; the choice is made on ``s + correction`` (where the
+    ``s = softmax(z)`` over all experts, or (``score="sigmoid"``) each expert's ``sigmoid(z)``; the choice is made on ``s + correction`` (where the
     model has one), restricted, with groups, to the experts of the ``group_keep`` groups (of
     ``group_count`` equal groups of neighbours) whose best choice score is largest; the chosen
-    experts' outputs are summed with their scores ``s`` as weights (not renormalised).
+    experts' outputs are summed with their scores ``s`` as weights (not renormalised); with
+    ``weight_input`` the weight multiplies the expert's input instead: the sum of ``expert(s * h)``.
     Routing, the experts' layout and their products all run on the device
     (csrc/moe.cu): a step's launches follow from its token count alone.
     Experts' tensors: ``gate_up_weight`` [experts * 2 * inner, hidden] (per expert the gate rows,
@@ -81,7 +82,10 @@ class MixtureOfExperts(Part):
 
     def __init__(self, hidden_size: int, inner_size: int, num_experts: int, top: int, group_count: int = 1,
                  group_keep: int = 1, gate: str = "silu", alpha: float = 1.0, limit: float = 0.0,
-                 correction: bool = False) -> None:
+                 correction: bool = False, score: str = "softmax", weight_input: bool = False) -> None:
+        if score not in K.MOE_SCORES:
+            raise ValueError(f"mixture of experts: score {score!r}; one of {sorted(K.MOE_SCORES)}")
+        self.score, self.weight_input = K.MOE_SCORES[score], bool(weight_input)
         if hidden_size % 8:
             raise ValueError(f"mixture of experts: the width {hidden_size} must be a multiple of 8")
         if not 0 < top <= num_experts or num_experts > 2048:
@@ -117,17 +121,20 @@ class MixtureOfExperts(Part):
         counts = ws.get_zeroed("moe_counts", (E,), i32)
         fill = ws.get_zeroed("moe_fill", (E,), i32)
         K.moe_select(z, self.correction, top=top, group_count=self.group_count, group_keep=self.group_keep, ids=ids,
-                     weights=weights, counts=counts)
+                     weights=weights, counts=counts, score=self.score)
         offsets = ws.get("moe_offsets", (E + 1,), i32)
         tiles = ws.get("moe_tiles", (K.moe_max_tiles(n * top, E) * 3,), i32)
         meta = ws.get("moe_meta", (4,), i32)
         row_token = ws.get("moe_row_token", (n * top,), i32)
         place_of = ws.get("moe_place_of", (n * top,), i32)
-        K.moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, n_tokens=n, n_experts=E, top=top)
+        by_place = ws.get("moe_place_weight", (n * top,), torch.float32) if self.weight_input else None
+        K.moe_plan(ids, counts, fill, offsets, tiles, meta, row_token, place_of, n_tokens=n, n_experts=E, top=top,
+                   weights=weights if self.weight_input else None, place_weight=by_place)
         act = ws.get("moe_inner", (n * top, f), ctx.act_dtype)
         eo = ws.get("moe_expert_out", (n * top, hid), torch.float32)
-        K.moe_experts(h, self.gate_up_weight, self.down_weight, tiles, meta, row_token, place_of, weights, act, eo, x,
-                      n_experts=E, top=top, ff=f, gate=self.gate, alpha=self.alpha, limit=self.limit, add=add)
+        K.moe_experts(h, self.gate_up_weight, self.down_weight, tiles, meta, row_token, place_of,
+                      None if self.weight_input else weights, act, eo, x, n_experts=E, top=top, ff=f, gate=self.gate,
+                      alpha=self.alpha, limit=self.limit, add=add, place_weight=by_place)
 
 
 @register_part("feed_forward", "token_gated_input")

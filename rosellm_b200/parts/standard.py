@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from .base import KVCacheSpec, ParamSpec, Part, register_part
+from .base import KVCacheSpec, ParamSpec, Part, StateSpec, register_part
 
 
 @register_part("position", "none")
@@ -110,6 +110,40 @@ class TokenEmbedding(Part):
         return x
 
 
+@register_part("embedding", "token_pair_table")
+class TokenPairEmbedding(Part):
+    """``x = table[token] + pair_table[(previous token * mul_prev + token * mul_cur) mod buckets]`` (+ the
+    position table's row): a second, hashed table indexed by the pair of neighbouring tokens; a
+    sequence's first token takes the table's last row, number ``buckets``.
+
+    The previous token of a portion's first token is the request's own state (one int32 in its
+    state slot, kept up to date by the kernel), so a prompt may be cut anywhere."""
+
+    graph_safe = True
+    launches_replayable = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, buckets: int, mul_prev: int, mul_cur: int) -> None:
+        if buckets <= 0:
+            raise ValueError("token pair table: buckets must be positive")
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.weight = self.pair_weight = None
+
+    def param_specs(self):
+        return [ParamSpec("weight", (self.vocab_size, self.hidden_size)),
+                ParamSpec("pair_weight", (self.buckets + 1, self.hidden_size))]
+
+    def state_spec(self):
+        return StateSpec((1,), torch.int32)
+
+    def forward(self, ctx, position) -> torch.Tensor:
+        x = ctx.workspace.get("residual", (ctx.n_tokens, self.hidden_size), torch.float32)
+        K.embed_pair(ctx.token_ids, ctx.positions, ctx.req_of_token, ctx.q_start, ctx.slots, self.weight,
+                     position.table(), self.pair_weight, x, ctx.state("embedding"), buckets=self.buckets,
+                     mul_prev=self.mul_prev, mul_cur=self.mul_cur, feedback=ctx.extras.get("token_feedback"))
+        return x
+
+
 @register_part("norm", "layer_norm")
 class LayerNorm(Part):
     """``(x - mean) * rsqrt(var + eps) * weight + bias`` over the last dimension
@@ -146,7 +180,9 @@ class LayerNorm(Part):
 
 @register_part("norm", "rms_norm")
 class RMSNorm(Part):
-    """``x / sqrt(mean(x^2) + eps) * weight`` over the last dimension, in float32.
+    """``x / sqrt(mean(x^2) + eps) * (weight_offset + weight)`` over the last dimension, in float32
+    (``weight_offset`` 1 for scales that are stored around zero; the sum is formed once, when the
+    weights are bound).
 
     ``forward`` normalises rows of the stream for a consumer (a head, a pre-norm block).
     ``add_to`` serves blocks that normalise a sublayer's output instead of its input:
@@ -156,15 +192,21 @@ class RMSNorm(Part):
     graph_safe = True
     launches_replayable = True
 
-    def __init__(self, hidden_size: int, eps: float) -> None:
+    def __init__(self, hidden_size: int, eps: float, weight_offset: float = 0.0) -> None:
         if eps <= 0:
             raise ValueError("the norm's eps must be positive")
         self.hidden_size = hidden_size
         self.eps = float(eps)
+        self.weight_offset = float(weight_offset)
         self.weight = None
 
     def param_specs(self):
-        return [ParamSpec("weight", (self.hidden_size,), kind="vector", init="ones")]
+        return [ParamSpec("weight", (self.hidden_size,), kind="vector", init="zeros" if self.weight_offset else "ones")]
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.weight_offset:
+            self.weight = self.weight + self.weight_offset
 
     def forward(self, ctx, x, rows=None, n_rows=None, name="normed", defer: bool = False):
         n = x.shape[0] if rows is None else int(n_rows)
@@ -174,6 +216,17 @@ class RMSNorm(Part):
 
     def add_to(self, ctx, y, x, mult: float, copy=None) -> None:
         K.rmsnorm_add(y, self.weight, self.eps, x, mult, copy)
+
+    def add_then_norm(self, ctx, y, x, following: "RMSNorm", name: str = "normed"):
+        """``x += norm(y)`` and, in the same pass, the new rows normalised by ``following`` (the norm
+        ahead of the next sublayer) in the activation dtype."""
+        out = ctx.workspace.get(name, tuple(x.shape), ctx.act_dtype)
+        if self.hidden_size > K.RMSNORM_ADD_NORM_MAX_WIDTH:
+            K.rmsnorm_add(y, self.weight, self.eps, x, 1.0, None)
+            K.rmsnorm(x, following.weight, following.eps, out)
+        else:
+            K.rmsnorm_add_norm(y, self.weight, self.eps, x, following.weight, following.eps, out)
+        return out
 
 
 _NARROW_PARTS: dict[tuple, int] = {}  # (request-head pairs, keys, bytes a key, blocks at once) -> parts, as computed before
@@ -517,6 +570,38 @@ class NormedSublayersBlock(Part):
         if self.has_token_input:
             layer.token_input.forward(ctx, h, y, add=False)
             layer.norm_token_input.add_to(ctx, y, x, self.mult, copy)
+
+
+@register_part("block", "pre_post_norm")
+class PrePostNormBlock(Part):
+    """Norms on both sides of every sublayer: ``x += norm_out(mixer(norm(x)))``, then (where the layer has
+    a feed-forward) ``x += norm_out(feed_forward(norm(x)))``, four norms of their own.  The norm behind
+    the mixer and the norm ahead of the feed-forward are one kernel."""
+
+    graph_safe = True
+    launches_replayable = True
+
+    def __init__(self, feed_forward: bool = True) -> None:
+        self.has_feed_forward = bool(feed_forward)
+        self.uses = {"norm_mixer": "norm", "mixer": "mixer", "norm_mixer_out": "norm"}
+        if feed_forward:
+            self.uses.update(norm_feed_forward="norm", feed_forward="feed_forward", norm_feed_forward_out="norm")
+
+    def forward(self, ctx, run, layer, x) -> None:
+        h = layer.norm_mixer.forward(ctx, x)
+        y = ctx.workspace.get("sublayer_out", tuple(x.shape), torch.float32)
+        layer.mixer.forward(ctx, run, h, y, add=False)
+        if not self.has_feed_forward:
+            layer.norm_mixer_out.add_to(ctx, y, x, 1.0)
+            return
+        fused = getattr(layer.norm_mixer_out, "add_then_norm", None)
+        if fused is not None and isinstance(layer.norm_feed_forward, RMSNorm):
+            h = fused(ctx, y, x, layer.norm_feed_forward)
+        else:
+            layer.norm_mixer_out.add_to(ctx, y, x, 1.0)
+            h = layer.norm_feed_forward.forward(ctx, x)
+        layer.feed_forward.forward(ctx, h, y, add=False)
+        layer.norm_feed_forward_out.add_to(ctx, y, x, 1.0)
 
 
 @register_part("head", "tied_to_embedding")

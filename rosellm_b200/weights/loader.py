@@ -137,8 +137,8 @@ def match_tensors(
             t = have.get(name)
             if t is None:
                 continue
-            if tuple(t.shape) != shape:
-                wrong_shape.append((name, shape, tuple(t.shape)))
+            if len(t.shape) != len(shape) or any(e != -1 and e != g for e, g in zip(shape, t.shape)):
+                wrong_shape.append((name, shape, tuple(t.shape)))  # an extent of -1 takes what the file has
             if p.spec.kind == "int_table":
                 if t.dtype.is_floating_point:
                     wrong_dtype.append((name, f"integer table stored as {t.dtype}"))

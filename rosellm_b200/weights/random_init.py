@@ -47,6 +47,9 @@ def random_tensors(
         if p.spec.kind == "int_table":
             raise ValueError(f"{p.file_name}: no random rule for integer tables")
         for name, shape in p.sources():  # a tensor the file holds in pieces: each piece by its own name
+            if any(int(e) < 0 for e in shape):
+                raise ValueError(f"{name}: the shape {list(shape)} leaves an extent to the file; random weights "
+                                 "need it given in the configuration")
             g = _generator_for(seed, name)
             noise = torch.randn(shape, generator=g, dtype=torch.float32) * std
             if p.spec.init == "ones":
