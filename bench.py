@@ -54,6 +54,10 @@ def parse_args():
     p.add_argument("--logits-then-sample", action="store_true",
                    help="write logits and sample from them in a kernel of its own, also where the head's product "
                         "could choose the tokens (for comparisons)")
+    p.add_argument("--compare-porovik", action="store_true",
+                   help="instead of the default workload: prefill and decode of the Porovik design (biased attention, "
+                        "delta-rule and gated recurrences, dense and expert feed-forwards) beside GPT-2 at equal width, "
+                        "depth and vocabulary")
     p.add_argument("--compare-lebedra", action="store_true",
                    help="instead of the default workload: prefill and decode of the Lebedra design (latent attention, "
                         "mixture of experts) beside GPT-2 of equal width, depth and vocabulary, at layer sizes of "
@@ -671,6 +675,70 @@ def compare_lebedra(args):
     return 0
 
 
+# Layer sizes for --compare-porovik: width; attention heads, key/value heads, key and value size; heads and
+# size of the delta rule (square states) and its decay rank; heads, key and value size of the gated
+# recurrence; dense inner size; experts, top, expert inner size.
+POROVIK_SIZES = {
+    "1024": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, d_heads=16, d_dim=64, d_rank=64, g_heads=8, g_dim=128,
+                 g_vdim=128, ff=4096, experts=16, top=2, expert_ff=1024),
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, d_heads=16, d_dim=128, d_rank=96, g_heads=16,
+                 g_dim=128, g_vdim=128, ff=8192, experts=32, top=4, expert_ff=1408),
+}
+
+
+def porovik_config(z: dict, layers: int, vocab: int, positions: int):
+    """Mixers in turn (attention, delta rule, gated recurrence); feed-forwards dense and experts in turn."""
+    from rosellm_b200.config.porovik import PorovikConfig
+
+    mixers = [
+        ("attention", {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                       "scale": z["dim"] ** -0.5, "q_temp": {"coef": 0.5, "every": 128}, "v_mix": True}),
+        ("general_delta", {"heads": z["d_heads"], "dim": z["d_dim"], "decay_rank": z["d_rank"]}),
+        ("hgrn2", {"heads": z["g_heads"], "dim": z["g_dim"], "vdim": z["g_vdim"]}),
+    ]
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    return PorovikConfig.from_dict({
+        "architecture": "Porovik", "vocab": vocab, "width": z["width"], "max_positions": positions, "norm": {"eps": 1e-5},
+        "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
+        "layers": [{"type": mixers[i % 3][0], "mixer": mixers[i % 3][1],
+                    "mlp": moe if i % 2 else {"kind": "dense", "ff": z["ff"]}} for i in range(layers)]})
+
+
+def compare_porovik(args):
+    """Prefill (2 x 1024 tokens) and decode (batch 8 and 64, 512 cached tokens) of Porovik and of GPT-2 at
+    equal width, depth and vocabulary: device time by CUDA events, as the default workload."""
+    layers, vocab, positions = 6, 32000, 1024
+    clocks = Clocks()
+    clocks.start()
+    out = {"metric": "prefill and decode of Porovik beside GPT-2 at equal width", "unit": "tokens/s", "n_gpus": 1,
+           "steps": args.steps, "warmup": args.warmup, "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+           "data": "synthetic (random token ids, random weights)", "layers": layers, "vocab": vocab, "sizes": {}}
+    for name, z in POROVIK_SIZES.items():
+        row = {}
+        gpt2 = dict(n_layer=layers, n_embd=z["width"], n_head=z["width"] // 64, n_inner=4 * z["width"],
+                    vocab_size=vocab, n_positions=positions, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+        for label, cfg in (("porovik", porovik_config(z, layers, vocab, positions)), ("gpt2", gpt2)):
+            h = Harness(cfg, args.dtype, 64, graphs=not args.no_graphs)
+            try:
+                pms = h.prefill()
+                rec = {"prefill_2x1024_ms": round(pms, 4), "prefill_tok_s": round(2048 / (pms * 1e-3), 1),
+                       "weight_mb": round(h.runner.model.weight_bytes() / 1e6, 1)}
+                for b in (8, 64):
+                    ms, launches, gms, _ = h.device_decode(b, args.context, max(16, args.steps // 2), max(4, args.warmup // 2))
+                    rec[f"decode_b{b}_ms"] = round(ms, 4)
+                    rec[f"decode_b{b}_tok_s"] = round(b / (ms * 1e-3), 1)
+                    rec[f"decode_b{b}_launches"] = launches
+                    if gms is not None:
+                        rec[f"decode_b{b}_graph_ms"] = round(gms, 4)
+                row[label] = rec
+            finally:
+                h.close()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
@@ -678,6 +746,8 @@ def main():
         sys.exit(2)
     if args.compare_lebedra:
         return compare_lebedra(args)
+    if args.compare_porovik:
+        return compare_porovik(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -103,23 +103,61 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   const int last_pos = pos0 + n_tok - 1;
   const T* pool = reinterpret_cast<const T*>(p.pool);
   const int* table = p.block_table + (size_t)slot * p.ldt;
-  for (int j0 = 0; j0 <= last_pos; j0 += BA_KEYS) {
-    __syncthreads();  // the tile before has been used (and, the first time, the queries are in place)
-    for (int jj = warp; jj < BA_KEYS; jj += BA_THREADS / 32) {
-      const int j = j0 + jj;
+  // Where each key of a tile lies (null: beyond the block's last position, or no page): looked up by one
+  // thread a key for the tile AFTER the one being copied, so that the copies themselves, 16 bytes a thread
+  // and several in flight, depend on nothing but shared memory.
+  __shared__ const T* key_src[2][BA_KEYS];
+  auto locate = [&](int j0, int buf) {
+    if (tid < BA_KEYS) {
+      const int j = j0 + tid;
       const T* src = nullptr;
       if (j <= last_pos) {
         const int lp = j / p.page_size;
         const int page = lp < p.max_pages ? table[lp] : -1;
-        if (page < 0) {
-          if (lane == 0) atomicOr(p.status, RL_STATUS_BAD_PAGE);
-        } else {
+        if (page < 0)
+          atomicOr(p.status, RL_STATUS_BAD_PAGE);
+        else
           src = pool + (((size_t)page * p.n_kv + g) * p.page_size + (j - lp * p.page_size)) * p.row;
-        }
       }
-      for (int d = lane; d < dk; d += 32) Ks[jj * ldk_s + d] = src != nullptr ? to_f32(src[d]) : 0.f;
-      for (int c = lane; c < ldv_s; c += 32) Vs[jj * ldv_s + c] = (src != nullptr && c < dv) ? to_f32(src[p.v_at + c]) : 0.f;
+      key_src[buf][tid] = src;
     }
+  };
+  constexpr int EV = 16 / (int)sizeof(T);  // elements of a 16-byte piece
+  const bool vec = dk % EV == 0 && dv % EV == 0 && p.row % EV == 0 && p.v_at % EV == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.pool) & 15) == 0;
+  for (int i = tid; i < BA_KEYS * ldv_s; i += BA_THREADS) Vs[i] = 0.f;  // the fill beyond dv stays zero
+  locate(0, 0);
+  int buf = 0;
+  for (int j0 = 0; j0 <= last_pos; j0 += BA_KEYS, buf ^= 1) {
+    __syncthreads();  // the tile before has been used; this tile's places (and, the first time, the queries) are known
+    if (vec) {
+      const int kp = dk / EV, vp = dv / EV, per_key = kp + vp;
+#pragma unroll 4
+      for (int i = tid; i < BA_KEYS * per_key; i += BA_THREADS) {
+        const int jj = i / per_key, piece = i - jj * per_key;
+        const T* src = key_src[buf][jj];
+        const bool is_v = piece >= kp;
+        const int at = is_v ? (piece - kp) * EV : piece * EV;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (src != nullptr) raw = *reinterpret_cast<const uint4*>(src + (is_v ? p.v_at : 0) + at);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        float* dst = is_v ? Vs + jj * ldv_s + at : Ks + jj * ldk_s + at;
+#pragma unroll
+        for (int x = 0; x < EV; ++x) dst[x] = to_f32(e[x]);
+      }
+    } else {
+      const int per_key = dk + dv;
+#pragma unroll 4
+      for (int i = tid; i < BA_KEYS * per_key; i += BA_THREADS) {
+        const int jj = i / per_key, c = i - jj * per_key;
+        const T* src = key_src[buf][jj];
+        const bool is_v = c >= dk;
+        const float val = src != nullptr ? to_f32(src[is_v ? p.v_at + c - dk : c]) : 0.f;
+        if (is_v) Vs[jj * ldv_s + c - dk] = val;
+        else Ks[jj * ldk_s + c] = val;
+      }
+    }
+    locate(j0 + BA_KEYS, buf ^ 1);
     __syncthreads();
     float s[2][4] = {};
     const float* q0 = Qs + (ty * 2) * ldq_s;

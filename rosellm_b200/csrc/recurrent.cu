@@ -1,26 +1,27 @@
 // Mixers with a matrix-valued state per request and head: S_t = diag(w_t) S_(t-1) [- (a_t * u_t)(u_t^T S_(t-1))]
 // + k_t v_t^T, o_t = S_t^T r_t, the state [dk, dv] in float32, carried from step to step in a state slot.
 //
-// Two forms share the kernel (`recurrence_kernel<MODE, ...>`):
-//   MODE 0, the generalized delta rule: per key channel a decay w = exp(-decay_scale * sigmoid(w0 + W2 tanh(p)))
+// Two forms share the kernels (MODE):
+//   0, the generalized delta rule: per key channel a decay w = exp(-decay_scale * sigmoid(w0 + W2 tanh(p)))
 //     (p: a low-rank projection of the layer's input), a removal rate a = sigmoid(a' + a_bias), the unit key
 //     u = k / sqrt(sum k^2 + unit_eps); the removal term and the decay both read the old state.  Output: each
 //     head's o divided by its root mean square, times a weight per (head, column), times sigmoid(g).
-//   MODE 1, a gated linear recurrence in which the forget gate also decides what is written: f = l + (1 - l) *
+//   1, a gated linear recurrence in which the forget gate also decides what is written: f = l + (1 - l) *
 //     sigmoid(f' + f_bias), w = f, k = 1 - f, r = silu(q'), no removal.  Output: each head's o RMS-normed with
 //     a weight per column that the heads share.
 //
-// The inputs are columns of one float32 matrix (the packed projections of the layer's input).  A block owns one
-// (request, head): thread j keeps column j of the state in registers, so a token costs no exchange between
-// threads.  Tokens are taken in chunks: the block first turns the chunk's projections into the vectors of the
-// recurrence (all of it in float32: sigmoids, exponentials, the unit key, the low-rank product), a warp a token,
-// into shared memory; then every thread walks the chunk's tokens reading those vectors as broadcasts; then, a
-// warp a token again, the chunk's outputs are normalised, gated and written in the activation type.
+// The inputs are columns of one float32 matrix (the packed projections of the layer's input).  Three kernels:
+//   `recurrence_prep_kernel`, a block a token: everything that does not depend on the state (sigmoids,
+//     exponentials, the low-rank product, the unit key), in float32, into one record per (head, token):
+//     [w | k | r (| u | a*u)] of DKP entries each, then the token's values (DVP entries);
+//   `recurrence_seq_kernel`, a block a (request, head): the only sequential part.  Four neighbouring lanes share
+//     a column of the state, each holding a quarter of its rows in registers; a token costs them two reductions
+//     over the four lanes (u^T S and S^T r); a block takes up to 64 columns, further blocks the rest.  The records of a chunk of tokens are one contiguous piece of memory,
+//     copied into shared memory with cp.async while the chunk before is worked on;
+//   `recurrence_out_kernel`, a warp a (token, head): the head's norm, weight and gate, in the activation type.
 #include "common.cuh"
 
 namespace rl {
-
-constexpr int REC_CHUNK = 16;  // tokens a chunk
 
 struct RecurParams {
   const float* proj;  // [tokens, ldp]
@@ -28,7 +29,7 @@ struct RecurParams {
   int off_r, off_k, off_v, off_a, off_g, off_w;  // first column of each projection (-1: the form has none)
   const float* a_bias;      // [heads * dk]: the removal rate's bias (0), the forget gate's bias (1)
   const float* w0;          // [heads * dk]: the decay's bias (0), the forget gate's lower bound (1)
-  const float* w2;          // [heads * dk, rank] (0)
+  const float* w2t;         // [rank, heads * dk] (0): the low-rank product's second matrix, transposed
   int rank;
   const float* out_weight;  // [heads * dv] (0), [dv] (1)
   float* state;             // [slots, heads, dk, dv]
@@ -36,201 +37,290 @@ struct RecurParams {
   long ldo;
   const int* q_start;
   const int* slots;
-  int n_heads, dk, dv;
+  float* prep;  // [heads, tokens, rec]
+  float* oraw;  // [tokens, heads * dv]
+  int n_tokens, n_heads, dk, dv, dkp, dvp, rec;
   float eps, decay_scale, unit_eps;
 };
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-template <int MODE, int DKMAX, typename TOut>
-__global__ __launch_bounds__(256) void recurrence_kernel(const RecurParams p) {
-  extern __shared__ __align__(16) float rec_s[];
+// dynamic shared memory: tanh of the low-rank input [rank], k [heads * dk], a [heads * dk] (MODE 0)
+template <int MODE>
+__global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams p) {
+  extern __shared__ float prep_s[];
+  pdl_begin();
+  const int tok = blockIdx.x;
+  const int C = p.n_heads * p.dk, dk = p.dk, dkp = p.dkp;
+  const float* row = p.proj + (size_t)tok * p.ldp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  auto record = [&](int head) { return p.prep + ((size_t)head * p.n_tokens + tok) * p.rec; };
+  if (MODE == 0) {
+    float* Ls = prep_s;
+    float* Ks = Ls + p.rank;
+    float* As = Ks + C;
+    for (int r = threadIdx.x; r < p.rank; r += blockDim.x) Ls[r] = tanhf(row[p.off_w + r]);
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float wl = p.w0[c];
+      for (int q = 0; q < p.rank; ++q) wl = fmaf(p.w2t[(size_t)q * C + c], Ls[q], wl);
+      const int head = c / dk, i = c - head * dk;
+      float* rec = record(head);
+      const float k = row[p.off_k + c];
+      rec[i] = expf(-p.decay_scale * sigmoidf_(wl));
+      rec[dkp + i] = k;
+      rec[2 * dkp + i] = row[p.off_r + c];
+      Ks[c] = k;
+      As[c] = sigmoidf_(row[p.off_a + c] + p.a_bias[c]);
+    }
+    __syncthreads();
+    for (int head = warp; head < p.n_heads; head += n_warps) {
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) ss = fmaf(Ks[head * dk + i], Ks[head * dk + i], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss + p.unit_eps);
+      float* rec = record(head);
+      for (int i = lane; i < dkp; i += 32) {
+        const float u = i < dk ? Ks[head * dk + i] * inv : 0.f;
+        rec[3 * dkp + i] = u;
+        rec[4 * dkp + i] = i < dk ? As[head * dk + i] * u : 0.f;
+        if (i >= dk) rec[i] = rec[dkp + i] = rec[2 * dkp + i] = 0.f;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < p.n_heads * dkp; c += blockDim.x) {
+      const int head = c / dkp, i = c - head * dkp;
+      float w = 0.f, k = 0.f, r = 0.f;
+      if (i < dk) {
+        const int ch = head * dk + i;
+        const float l = p.w0[ch];
+        const float f = l + (1.0f - l) * sigmoidf_(row[p.off_a + ch] + p.a_bias[ch]);
+        const float q = row[p.off_r + ch];
+        w = f;
+        k = 1.0f - f;
+        r = q * sigmoidf_(q);
+      }
+      float* rec = record(head);
+      rec[i] = w;
+      rec[dkp + i] = k;
+      rec[2 * dkp + i] = r;
+    }
+  }
+  constexpr int NV = MODE == 0 ? 5 : 3;
+  for (int c = threadIdx.x; c < p.n_heads * p.dvp; c += blockDim.x) {
+    const int head = c / p.dvp, j = c - head * p.dvp;
+    record(head)[NV * dkp + j] = j < p.dv ? row[p.off_v + head * p.dv + j] : 0.f;
+  }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// DKQ: state rows a thread (a quarter of DKP).  Thread (column = tid / 4, part = tid % 4) holds the rows
+// 16 m + 4 part + e (m < DKQ / 4, e < 4) of its column: the four parts read neighbouring 16-byte pieces
+// of a record's vectors.  chunk: tokens a buffer of shared memory.
+constexpr int REC_COLS = 64;  // state columns a block (four threads each)
+
+template <int MODE, int DKQ>
+__global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const RecurParams p, int chunk) {
+  extern __shared__ __align__(16) float seq_s[];
   pdl_begin();
   const int req = blockIdx.x, head = blockIdx.y;
   const int slot = p.slots[req];
   if (slot < 0) return;  // a padding row of a captured step
+  constexpr int NV = MODE == 0 ? 5 : 3;
+  constexpr int DKP = 4 * DKQ;
   const int t0 = p.q_start[req], t1 = p.q_start[req + 1];
-  const int dk = p.dk, dv = p.dv, j = threadIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  const int dvp = (dv + 3) & ~3, rankp = p.rank > 0 ? p.rank : 1;
-  // shared memory: W, K, R (, U, AU) [chunk][DKMAX]; V, O [chunk][dvp]; the low-rank input [chunk][rank]
-  constexpr int NVEC = MODE == 0 ? 5 : 3;
-  float* Ws = rec_s;
-  float* Ks = Ws + REC_CHUNK * DKMAX;
-  float* Rs = Ks + REC_CHUNK * DKMAX;
-  float* Us = Rs + REC_CHUNK * DKMAX;                 // MODE 0 only
-  float* AUs = Us + REC_CHUNK * DKMAX;                // MODE 0 only
-  float* Vs = rec_s + NVEC * REC_CHUNK * DKMAX;
-  float* Os = Vs + REC_CHUNK * dvp;
-  float* Ls = Os + REC_CHUNK * dvp;
-  float S[DKMAX];
+  const int dk = p.dk, dv = p.dv, rec = p.rec;
+  const int col = blockIdx.z * REC_COLS + (threadIdx.x >> 2), part = threadIdx.x & 3;
+  float S[DKQ];
   float* st = p.state + (((size_t)slot * p.n_heads + head) * dk) * dv;
 #pragma unroll
-  for (int i = 0; i < DKMAX; ++i) S[i] = (i < dk && j < dv) ? st[(size_t)i * dv + j] : 0.f;
-  const int c0 = head * dk;  // the head's first key channel
-  for (int tc = t0; tc < t1; tc += REC_CHUNK) {
-    const int nt = min(REC_CHUNK, t1 - tc);
-    __syncthreads();  // the chunk before has been read
-    for (int t = warp; t < nt; t += n_warps) {
-      const float* row = p.proj + (size_t)(tc + t) * p.ldp;
+  for (int k = 0; k < DKQ; ++k) {
+    const int r = (k >> 2) * 16 + 4 * part + (k & 3);
+    S[k] = (r < dk && col < dv) ? st[(size_t)r * dv + col] : 0.f;
+  }
+  const float* src = p.prep + ((size_t)head * p.n_tokens + t0) * rec;
+  const int n_chunks = (t1 - t0 + chunk - 1) / chunk;
+  auto fetch = [&](int c) {
+    const int nt = min(chunk, t1 - t0 - c * chunk);
+    float* dst = seq_s + (size_t)(c & 1) * chunk * rec;
+    const float* from = src + (size_t)c * chunk * rec;
+    for (int i = threadIdx.x; i < nt * rec / 4; i += blockDim.x) cp_async16(dst + 4 * i, from + 4 * i);
+    cp_async_commit();
+  };
+  fetch(0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) {
+      fetch(c + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int nt = min(chunk, t1 - t0 - c * chunk);
+    const float* buf = seq_s + (size_t)(c & 1) * chunk * rec;
+    for (int t = 0; t < nt; ++t) {
+      const float* r_ = buf + (size_t)t * rec;
+      const float4* W4 = reinterpret_cast<const float4*>(r_);
+      const float4* K4 = reinterpret_cast<const float4*>(r_ + DKP);
+      const float4* R4 = reinterpret_cast<const float4*>(r_ + 2 * DKP);
+      const float4* U4 = reinterpret_cast<const float4*>(r_ + 3 * DKP);
+      const float4* AU4 = reinterpret_cast<const float4*>(r_ + 4 * DKP);
+      const float vj = col < p.dvp ? r_[NV * DKP + col] : 0.f;
+      float pj = 0.f;
       if (MODE == 0) {
-        for (int r = lane; r < p.rank; r += 32) Ls[t * rankp + r] = tanhf(row[p.off_w + r]);
-        __syncwarp();
-        float ss = 0.f;
-        for (int i = lane; i < DKMAX; i += 32) {
-          float w = 0.f, k = 0.f, r = 0.f, a = 0.f;
-          if (i < dk) {
-            const int c = c0 + i;
-            k = row[p.off_k + c];
-            r = row[p.off_r + c];
-            float wl = p.w0[c];
-            const float* w2 = p.w2 + (size_t)c * p.rank;
-            for (int q = 0; q < p.rank; ++q) wl = fmaf(w2[q], Ls[t * rankp + q], wl);
-            w = expf(-p.decay_scale * sigmoidf_(wl));
-            a = sigmoidf_(row[p.off_a + c] + p.a_bias[c]);
-          }
-          Ws[t * DKMAX + i] = w;
-          Ks[t * DKMAX + i] = k;
-          Rs[t * DKMAX + i] = r;
-          AUs[t * DKMAX + i] = a;
-          ss = fmaf(k, k, ss);
-        }
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss + p.unit_eps);
-        for (int i = lane; i < DKMAX; i += 32) {
-          const float u = Ks[t * DKMAX + i] * inv;
-          Us[t * DKMAX + i] = u;
-          AUs[t * DKMAX + i] *= u;
-        }
-      } else {
-        for (int i = lane; i < DKMAX; i += 32) {
-          float w = 0.f, k = 0.f, r = 0.f;
-          if (i < dk) {
-            const int c = c0 + i;
-            const float l = p.w0[c];
-            const float f = l + (1.0f - l) * sigmoidf_(row[p.off_a + c] + p.a_bias[c]);
-            const float q = row[p.off_r + c];
-            w = f;
-            k = 1.0f - f;
-            r = q * sigmoidf_(q);
-          }
-          Ws[t * DKMAX + i] = w;
-          Ks[t * DKMAX + i] = k;
-          Rs[t * DKMAX + i] = r;
-        }
-      }
-      for (int c = lane; c < dvp; c += 32) Vs[t * dvp + c] = c < dv ? row[p.off_v + head * dv + c] : 0.f;
-    }
-    __syncthreads();
-    if (j < dvp) {
-      for (int t = 0; t < nt; ++t) {
-        const float4* W4 = reinterpret_cast<const float4*>(Ws + t * DKMAX);
-        const float4* K4 = reinterpret_cast<const float4*>(Ks + t * DKMAX);
-        const float4* R4 = reinterpret_cast<const float4*>(Rs + t * DKMAX);
-        const float vj = Vs[t * dvp + j];
-        float pj = 0.f;
-        if (MODE == 0) {
-          const float4* U4 = reinterpret_cast<const float4*>(Us + t * DKMAX);
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-          for (int i = 0; i < DKMAX / 4; ++i) {
-            const float4 u = U4[i];
-            pj = fmaf(u.x, S[4 * i], fmaf(u.y, S[4 * i + 1], fmaf(u.z, S[4 * i + 2], fmaf(u.w, S[4 * i + 3], pj))));
-          }
+        for (int m = 0; m < DKQ / 4; ++m) {
+          const float4 u = U4[4 * m + part];
+          a0 = fmaf(u.x, S[4 * m], fmaf(u.y, S[4 * m + 1], a0));
+          a1 = fmaf(u.z, S[4 * m + 2], fmaf(u.w, S[4 * m + 3], a1));
         }
-        float o = 0.f;
-        const float4* AU4 = reinterpret_cast<const float4*>(AUs + t * DKMAX);
-#pragma unroll
-        for (int i = 0; i < DKMAX / 4; ++i) {
-          const float4 w = W4[i], k = K4[i], r = R4[i];
-          float4 au = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (MODE == 0) au = AU4[i];
-          float s0 = fmaf(w.x, S[4 * i], fmaf(-au.x, pj, k.x * vj));
-          float s1 = fmaf(w.y, S[4 * i + 1], fmaf(-au.y, pj, k.y * vj));
-          float s2 = fmaf(w.z, S[4 * i + 2], fmaf(-au.z, pj, k.z * vj));
-          float s3 = fmaf(w.w, S[4 * i + 3], fmaf(-au.w, pj, k.w * vj));
-          S[4 * i] = s0;
-          S[4 * i + 1] = s1;
-          S[4 * i + 2] = s2;
-          S[4 * i + 3] = s3;
-          o = fmaf(s0, r.x, fmaf(s1, r.y, fmaf(s2, r.z, fmaf(s3, r.w, o))));
-        }
-        Os[t * dvp + j] = o;
+        pj = a0 + a1;
+        pj += __shfl_xor_sync(0xffffffffu, pj, 1);
+        pj += __shfl_xor_sync(0xffffffffu, pj, 2);
       }
-    }
-    __syncthreads();
-    for (int t = warp; t < nt; t += n_warps) {
-      float ss = 0.f;
-      for (int c = lane; c < dv; c += 32) ss = fmaf(Os[t * dvp + c], Os[t * dvp + c], ss);
-      ss = warp_sum(ss);
-      const float rn = 1.0f / sqrtf(ss / (float)dv + p.eps);
-      const float* row = p.proj + (size_t)(tc + t) * p.ldp;
-      TOut* orow = reinterpret_cast<TOut*>(p.out) + (size_t)(tc + t) * p.ldo + (size_t)head * dv;
-      for (int c = lane; c < dv; c += 32) {
-        float v = Os[t * dvp + c] * rn;
-        if (MODE == 0)
-          v = v * p.out_weight[head * dv + c] * sigmoidf_(row[p.off_g + head * dv + c]);
-        else
-          v = v * p.out_weight[c];
-        orow[c] = from_f32<TOut>(v);
-      }
-    }
-  }
-  if (j < dv) {
+      float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < DKMAX; ++i)
-      if (i < dk) st[(size_t)i * dv + j] = S[i];
-  }
-}
-
-template <int MODE, int DKMAX, typename TOut>
-static int launch_recurrence(const RecurParams& p, int n_reqs, cudaStream_t stream) {
-  const int dvp = (p.dv + 3) & ~3;
-  const int threads = (dvp + 31) / 32 * 32;
-  const size_t smem = ((size_t)(MODE == 0 ? 5 : 3) * REC_CHUNK * DKMAX + 2 * REC_CHUNK * dvp +
-                       (size_t)REC_CHUNK * (p.rank > 0 ? p.rank : 1)) * sizeof(float);
-  auto kernel = recurrence_kernel<MODE, DKMAX, TOut>;
-  if (smem > 48 * 1024) {
-    static bool raised = false;
-    if (!raised) {
-      note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      raised = true;
+      for (int m = 0; m < DKQ / 4; ++m) {
+        const float4 w = W4[4 * m + part], k = K4[4 * m + part], r = R4[4 * m + part];
+        float4 au = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (MODE == 0) au = AU4[4 * m + part];
+        const float s0 = fmaf(w.x, S[4 * m], fmaf(-au.x, pj, k.x * vj));
+        const float s1 = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, pj, k.y * vj));
+        const float s2 = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, pj, k.z * vj));
+        const float s3 = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, pj, k.w * vj));
+        S[4 * m] = s0;
+        S[4 * m + 1] = s1;
+        S[4 * m + 2] = s2;
+        S[4 * m + 3] = s3;
+        o0 = fmaf(s0, r.x, fmaf(s1, r.y, o0));
+        o1 = fmaf(s2, r.z, fmaf(s3, r.w, o1));
+      }
+      float o = o0 + o1;
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (part == 0 && col < dv) p.oraw[(size_t)(t0 + c * chunk + t) * p.n_heads * dv + (size_t)head * dv + col] = o;
     }
+    __syncthreads();  // the buffer is free for the chunk after the next
   }
-  launch_pdl(kernel, dim3(n_reqs, p.n_heads), threads, smem, stream, p);
-  return 0;
+#pragma unroll
+  for (int k = 0; k < DKQ; ++k) {
+    const int r = (k >> 2) * 16 + 4 * part + (k & 3);
+    if (r < dk && col < dv) st[(size_t)r * dv + col] = S[k];
+  }
 }
 
 template <int MODE, typename TOut>
-static int dispatch_recurrence(const RecurParams& p, int n_reqs, cudaStream_t stream) {
-  if (p.dk <= 16) return launch_recurrence<MODE, 16, TOut>(p, n_reqs, stream);
-  if (p.dk <= 32) return launch_recurrence<MODE, 32, TOut>(p, n_reqs, stream);
-  if (p.dk <= 64) return launch_recurrence<MODE, 64, TOut>(p, n_reqs, stream);
-  if (p.dk <= 128) return launch_recurrence<MODE, 128, TOut>(p, n_reqs, stream);
-  return launch_recurrence<MODE, 256, TOut>(p, n_reqs, stream);
+__global__ __launch_bounds__(256) void recurrence_out_kernel(const RecurParams p) {
+  pdl_begin();
+  const int tok = blockIdx.x, dv = p.dv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const float* row = p.proj + (size_t)tok * p.ldp;
+  for (int head = warp; head < p.n_heads; head += n_warps) {
+    const float* o = p.oraw + (size_t)tok * p.n_heads * dv + (size_t)head * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(o[c], o[c], ss);
+    ss = warp_sum(ss);
+    const float rn = 1.0f / sqrtf(ss / (float)dv + p.eps);
+    TOut* orow = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
+    for (int c = lane; c < dv; c += 32) {
+      float v = o[c] * rn;
+      if (MODE == 0)
+        v = v * p.out_weight[head * dv + c] * sigmoidf_(row[p.off_g + head * dv + c]);
+      else
+        v = v * p.out_weight[c];
+      orow[c] = from_f32<TOut>(v);
+    }
+  }
+}
+
+template <int MODE, int DKQ>
+static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
+  // tokens a buffer: as many as two buffers of about 48 KB hold, at most 16
+  int chunk = (int)(48 * 1024 / ((size_t)p.rec * sizeof(float)));
+  chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
+  const size_t smem = (size_t)2 * chunk * p.rec * sizeof(float);
+  auto kernel = recurrence_seq_kernel<MODE, DKQ>;
+  if (smem > 48 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      raised = true;
+    }
+  }
+  const int col_blocks = (p.dv + REC_COLS - 1) / REC_COLS;
+  const int cols = (p.dv + col_blocks - 1) / col_blocks;  // the last block's share may be shorter
+  const int threads = col_blocks == 1 ? (4 * cols + 31) / 32 * 32 : 4 * REC_COLS;
+  launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), threads, smem, stream, p, chunk);
+}
+
+template <int MODE>
+static void dispatch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
+  switch (p.dkp) {
+    case 16: launch_seq<MODE, 4>(p, n_reqs, stream); break;
+    case 32: launch_seq<MODE, 8>(p, n_reqs, stream); break;
+    case 64: launch_seq<MODE, 16>(p, n_reqs, stream); break;
+    case 128: launch_seq<MODE, 32>(p, n_reqs, stream); break;
+    default: launch_seq<MODE, 64>(p, n_reqs, stream); break;
+  }
 }
 
 }  // namespace rl
 
+// The padded key size of a record's vectors (16, 32, 64, 128 or 256), the padded value size, and the floats a
+// record takes: what the caller sizes `prep` by (heads * tokens * record floats).
+RL_EXPORT int rl_recurrence_record(int mode, int dk, int dv, int* dkp, int* dvp, int* rec) {
+  if (mode < 0 || mode > 1 || dk <= 0 || dk > 256 || dv <= 0 || dv > 256) return -2;
+  int k = 16;
+  while (k < dk) k *= 2;
+  *dkp = k;
+  *dvp = (dv + 3) & ~3;
+  *rec = (mode == 0 ? 5 : 3) * k + *dvp;
+  return 0;
+}
+
 // mode 0: generalized delta rule; 1: gated recurrence (see the top of this file).  proj: float32 [tokens, ldp]
 // holding the projections at the given column offsets; state: float32 [slots, heads, dk, dv], read and written
 // for the step's requests (slot < 0: skipped); out: [tokens, heads * dv] of out_dtype, row stride ldo.
+// prep: float32 scratch [heads * tokens * record]; oraw: float32 scratch [tokens, heads * dv].
 RL_EXPORT int rl_recurrence(int mode, int out_dtype, const float* proj, long ldp, int off_r, int off_k, int off_v,
-                            int off_a, int off_g, int off_w, const float* a_bias, const float* w0, const float* w2,
+                            int off_a, int off_g, int off_w, const float* a_bias, const float* w0, const float* w2t,
                             int rank, const float* out_weight, float* state, void* out, long ldo, const int* q_start,
-                            const int* slots, int n_reqs, int n_heads, int dk, int dv, float eps, float decay_scale,
-                            float unit_eps, cudaStream_t stream) {
-  if (n_reqs <= 0) return 0;
-  if (mode < 0 || mode > 1 || n_heads <= 0 || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || rank < 0 || rank > 1024)
-    return -2;
-  if (n_heads > 65535) return -2;
-  rl::RecurParams p{proj, ldp, off_r, off_k, off_v, off_a, off_g, off_w, a_bias, w0, w2, rank, out_weight, state, out,
-                    ldo, q_start, slots, n_heads, dk, dv, eps, decay_scale, unit_eps};
+                            const int* slots, float* prep, float* oraw, int n_tokens, int n_reqs, int n_heads, int dk,
+                            int dv, float eps, float decay_scale, float unit_eps, cudaStream_t stream) {
+  if (n_reqs <= 0 || n_tokens <= 0) return 0;
+  int dkp, dvp, rec;
+  if (rl_recurrence_record(mode, dk, dv, &dkp, &dvp, &rec) != 0 || n_heads <= 0 || n_heads > 65535 || rank < 0) return -2;
+  rl::RecurParams p{proj, ldp, off_r, off_k, off_v, off_a, off_g, off_w, a_bias, w0, w2t, rank, out_weight, state, out,
+                    ldo, q_start, slots, prep, oraw, n_tokens, n_heads, dk, dv, dkp, dvp, rec, eps, decay_scale, unit_eps};
+  const size_t prep_smem = mode == 0 ? ((size_t)rank + 2 * (size_t)n_heads * dk) * sizeof(float) : 0;
+  if (prep_smem > 160 * 1024) return -2;
   if (mode == 0) {
-    if (out_dtype == RL_F32) rl::dispatch_recurrence<0, float>(p, n_reqs, stream);
-    else rl::dispatch_recurrence<0, __nv_bfloat16>(p, n_reqs, stream);
+    if (prep_smem > 48 * 1024) {
+      static bool raised = false;
+      if (!raised) {
+        rl::note_launch(cudaFuncSetAttribute(rl::recurrence_prep_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        raised = true;
+      }
+    }
+    rl::launch_pdl(rl::recurrence_prep_kernel<0>, n_tokens, 256, prep_smem, stream, p);
+    rl::dispatch_seq<0>(p, n_reqs, stream);
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<0, float>, n_tokens, 256, 0, stream, p);
+    else rl::launch_pdl(rl::recurrence_out_kernel<0, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
   } else {
-    if (out_dtype == RL_F32) rl::dispatch_recurrence<1, float>(p, n_reqs, stream);
-    else rl::dispatch_recurrence<1, __nv_bfloat16>(p, n_reqs, stream);
+    rl::launch_pdl(rl::recurrence_prep_kernel<1>, n_tokens, 256, 0, stream, p);
+    rl::dispatch_seq<1>(p, n_reqs, stream);
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<1, float>, n_tokens, 256, 0, stream, p);
+    else rl::launch_pdl(rl::recurrence_out_kernel<1, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
   }
   RL_CHECK_LAUNCH();
   return 0;

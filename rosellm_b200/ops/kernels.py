@@ -94,7 +94,7 @@ class _RecordingLib:
 
 _QUERIES = ("rl_gemm_tc_rows_fits", "rl_gemm_rows_smem_fits", "rl_mlp_fused_slice", "rl_attn_block_fused_fits", "rl_attn_block_fused_cluster",
             "rl_host_memory_on_device", "rl_latent_attention_fits", "rl_latent_decode_fits",
-            "rl_moe_max_tiles", "rl_bias_attention_shape")  # library functions that launch nothing
+            "rl_moe_max_tiles", "rl_bias_attention_shape", "rl_recurrence_record")  # library functions that launch nothing
 
 
 class recording:
@@ -169,7 +169,8 @@ def _lib() -> ctypes.CDLL:
         lib.rl_moe_experts.argtypes = [I, P, L, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, F, F, I, P]
         lib.rl_embed_pair.argtypes = [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, I, P]
         lib.rl_rmsnorm_add_norm.argtypes = [I, P, L, P, P, L, P, P, L, I, I, F, F, P]
-        lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, I, I, I, I, F, F, F, P]
+        lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, F, F, F, P]
+        lib.rl_recurrence_record.argtypes = [I, I, I, P, P, P]
         lib.rl_bias_attention_shape.argtypes = [I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
                                           F, F, I, P, P, P]
@@ -177,7 +178,7 @@ def _lib() -> ctypes.CDLL:
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
                      "rl_token_gate", "rl_moe_select", "rl_moe_plan", "rl_moe_max_tiles", "rl_moe_experts", "rl_embed_pair",
-                     "rl_rmsnorm_add_norm", "rl_recurrence", "rl_bias_attention_shape", "rl_bias_attention",
+                     "rl_rmsnorm_add_norm", "rl_recurrence", "rl_recurrence_record", "rl_bias_attention_shape", "rl_bias_attention",
                      "rl_bias_kv_store"):
             getattr(lib, name).restype = I
         for name in ("rl_copy_to_device", "rl_event_record", "rl_embed", "rl_layernorm", "rl_gemm_simt", "rl_gemm_tc", "rl_gemm_tc_sample", "rl_gemm_tc_cut", "rl_gemm_tc_rows", "rl_gemm_tc_rows_fits",
@@ -1231,34 +1232,52 @@ RMSNORM_ADD_NORM_MAX_WIDTH = 48 * 1024 // 4 - 64
 RECURRENCES = {"delta": 0, "gated": 1}
 
 
-def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, *, n_reqs: int, n_heads: int, dk: int,
-               dv: int, eps: float, a_bias, w0, out_weight, w2=None, rank: int = 0, decay_scale: float = 0.0,
+def recurrence_record(mode: int, dk: int, dv: int) -> int:
+    """Floats of the record that ``recurrence`` keeps per (head, token) in its ``prep`` scratch."""
+    a, b, c = c_int(0), c_int(0), c_int(0)
+    if _lib().rl_recurrence_record(int(mode), int(dk), int(dv), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)) != 0:
+        raise KernelError(f"recurrence: sizes not taken (key size {dk}, value size {dv}: up to 256 each)")
+    return c.value
+
+
+def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, prep, oraw, *, n_reqs: int, n_heads: int,
+               dk: int, dv: int, eps: float, a_bias, w0, out_weight, w2t=None, rank: int = 0, decay_scale: float = 0.0,
                unit_eps: float = 0.0) -> None:
     """One step of a recurrence over matrix states (csrc/recurrent.cu) for every request of the step.
     ``proj`` float32 [tokens, columns]: the packed projections, ``offsets`` the first column of
     ``r``, ``k``, ``v``, ``a``, ``g``, ``w`` (those the form has); ``state`` float32
-    [slots, heads, dk, dv]; ``out`` [tokens, heads * dv] float32 or bfloat16."""
+    [slots, heads, dk, dv]; ``out`` [tokens, heads * dv] float32 or bfloat16; ``prep`` float32 scratch of
+    heads * tokens * ``recurrence_record`` floats, ``oraw`` float32 scratch [tokens, heads * dv];
+    ``w2t`` float32 [rank, heads * dk]: the low-rank decay's second matrix, transposed."""
     _need(proj, "proj", torch.float32, contiguous=False)
     _need(state, "state", torch.float32)
     _need(out, "out", contiguous=False)
+    _need(prep, "prep", torch.float32)
+    _need(oraw, "oraw", torch.float32)
     for t, name in ((a_bias, "a_bias"), (w0, "w0"), (out_weight, "out_weight")):
         _need(t, name, torch.float32)
-    if w2 is not None:
-        _need(w2, "w2", torch.float32)
-        if tuple(w2.shape) != (n_heads * dk, rank):
+    n_tokens = proj.shape[0]
+    if w2t is not None:
+        _need(w2t, "w2t", torch.float32)
+        if tuple(w2t.shape) != (rank, n_heads * dk):
             raise KernelError("recurrence: the low-rank matrix has another shape")
-    if tuple(state.shape[1:]) != (n_heads, dk, dv) or out.shape[1] != n_heads * dv or proj.stride(1) != 1 or out.stride(1) != 1:
+    if tuple(state.shape[1:]) != (n_heads, dk, dv) or out.shape[1] != n_heads * dv or proj.stride(1) != 1 \
+            or out.stride(1) != 1 or out.shape[0] != n_tokens:
         raise KernelError("recurrence: shapes do not fit")
-    if mode == 0 and (w2 is None or rank <= 0):
+    if prep.numel() < n_heads * n_tokens * recurrence_record(mode, dk, dv) or oraw.numel() < n_tokens * n_heads * dv:
+        raise KernelError("recurrence: scratch too small")
+    if mode == 0 and (w2t is None or rank <= 0):
         raise KernelError("recurrence: the delta form needs its low-rank decay")
     off = [int(offsets.get(k, -1)) for k in ("r", "k", "v", "a", "g", "w")]
-    rc = _lib().rl_recurrence(int(mode), _code(out), _ptr(proj), proj.stride(0), *off, _ptr(a_bias), _ptr(w0), _ptr(w2),
+    rc = _lib().rl_recurrence(int(mode), _code(out), _ptr(proj), proj.stride(0), *off, _ptr(a_bias), _ptr(w0), _ptr(w2t),
                               int(rank), _ptr(out_weight), _ptr(state), _ptr(out), out.stride(0), _ptr(q_start),
-                              _ptr(slots), n_reqs, n_heads, dk, dv, float(eps), float(decay_scale), float(unit_eps),
-                              _stream())
+                              _ptr(slots), _ptr(prep), _ptr(oraw), n_tokens, n_reqs, n_heads, dk, dv, float(eps),
+                              float(decay_scale), float(unit_eps), _stream())
     if rc == -2:
         raise KernelError(f"recurrence: sizes not taken (key size {dk}, value size {dv}: up to 256 each)")
     _ok(rc, "recurrence")
+    global _launches
+    _launches += 2
 
 
 # ---- attention with a distance bias over rows of [key | value] -------------------------------------

@@ -1,7 +1,7 @@
 """Mixers that keep a matrix-valued state per request and head instead of a cache of keys.
 
 Both forms run one recurrence, ``S_t = diag(w_t) S_(t-1) [- (a_t * u_t)(u_t^T S_(t-1))] + k_t v_t^T`` and
-``o_t = S_t^T r_t``, on the kernel of csrc/recurrent.cu: the state is float32 ``[heads, key size, value
+``o_t = S_t^T r_t``, on the kernels of csrc/recurrent.cu: the state is float32 ``[heads, key size, value
 size]`` in the request's state slot (zero when the slot is taken), a step continues it for however many
 tokens the request brings, and everything between the projections and the output product is float32.
 
@@ -52,6 +52,12 @@ class _StateMixer(Part):
         buf = ctx.workspace.get_zeroed(f"state_mixer_out_{real}_{padded}", (ctx.n_tokens, padded), ctx.act_dtype)
         return buf, buf[:, :real]
 
+    def _scratch(self, ctx, mode: int, dk: int, dv: int):
+        n = ctx.n_tokens
+        prep = ctx.workspace.get("state_mixer_prep", (self.num_heads * n * K.recurrence_record(mode, dk, dv),), torch.float32)
+        oraw = ctx.workspace.get("state_mixer_raw", (n, self.num_heads * dv), torch.float32)
+        return prep, oraw
+
     def _pad_out_weight(self) -> None:
         self.out_padded = -(-self.out_width // 8) * 8
         if self.out_padded != self.out_width:
@@ -100,17 +106,20 @@ class DeltaRuleMixer(_StateMixer):
         names = ("r", "k", "v", "a", "g", "w")
         self.proj_weight, offs = pack_rows([t[n + "_weight"] for n in ("r", "k", "v", "a", "g", "w1")])
         self.offsets = dict(zip(names, offs))
-        self.w2_weight, self.a_bias, self.w0, self.out_norm = t["w2_weight"], t["a_bias"], t["w0"], t["out_norm"]
+        self.w2t_weight = t["w2_weight"].t().contiguous()  # [rank, channels]: the kernel's threads walk the channels
+        self.a_bias, self.w0, self.out_norm = t["a_bias"], t["w0"], t["out_norm"]
         self.out_weight = t["out_weight"]
         self._pad_out_weight()
 
     def forward(self, ctx, run, h, x, add: bool = True) -> None:
         proj = self._project(ctx, h)
         buf, view = self._out_buffer(ctx)
-        K.recurrence(K.RECURRENCES["delta"], proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
-                     ctx.q_start, ctx.slots, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.head_dim, dv=self.head_dim,
-                     eps=self.norm_eps, a_bias=self.a_bias, w0=self.w0, out_weight=self.out_norm, w2=self.w2_weight,
-                     rank=self.rank, decay_scale=self.decay_scale, unit_eps=self.unit_eps)
+        mode = K.RECURRENCES["delta"]
+        prep, oraw = self._scratch(ctx, mode, self.head_dim, self.head_dim)
+        K.recurrence(mode, proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
+                     ctx.q_start, ctx.slots, prep, oraw, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.head_dim,
+                     dv=self.head_dim, eps=self.norm_eps, a_bias=self.a_bias, w0=self.w0, out_weight=self.out_norm,
+                     w2t=self.w2t_weight, rank=self.rank, decay_scale=self.decay_scale, unit_eps=self.unit_eps)
         K.linear(buf, self.out_weight, None, x, residual=add)
 
 
@@ -149,7 +158,9 @@ class GatedRecurrenceMixer(_StateMixer):
     def forward(self, ctx, run, h, x, add: bool = True) -> None:
         proj = self._project(ctx, h)
         buf, view = self._out_buffer(ctx)
-        K.recurrence(K.RECURRENCES["gated"], proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
-                     ctx.q_start, ctx.slots, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.key_dim, dv=self.value_dim,
-                     eps=self.norm_eps, a_bias=self.f_bias, w0=self.lower, out_weight=self.out_norm)
+        mode = K.RECURRENCES["gated"]
+        prep, oraw = self._scratch(ctx, mode, self.key_dim, self.value_dim)
+        K.recurrence(mode, proj, self.offsets, ctx.state(run.state_key), buf if view is None else view,
+                     ctx.q_start, ctx.slots, prep, oraw, n_reqs=ctx.n_reqs, n_heads=self.num_heads, dk=self.key_dim,
+                     dv=self.value_dim, eps=self.norm_eps, a_bias=self.f_bias, w0=self.lower, out_weight=self.out_norm)
         K.linear(buf, self.out_weight, None, x, residual=add)

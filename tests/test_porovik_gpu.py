@@ -227,8 +227,11 @@ def _recurrence_case(mode, dtype, H, dk, dv, lens, cuts, seed, rank=4):
         kw = dict(n_reqs=len(ents), n_heads=H, dk=dk, dv=dv, eps=1e-5, a_bias=a_bias.to(DEV), w0=w0.to(DEV),
                   out_weight=out_w.to(DEV))
         if mode == "delta":
-            kw.update(w2=w2.to(DEV), rank=rank, decay_scale=math.exp(-0.5), unit_eps=1e-6)
-        K().recurrence(K().RECURRENCES[mode], pj, offs, state, out, dev(hb.q_start), dev(hb.slots), **kw)
+            kw.update(w2t=w2.t().contiguous().to(DEV), rank=rank, decay_scale=math.exp(-0.5), unit_eps=1e-6)
+        m = K().RECURRENCES[mode]
+        prep = torch.full((H * pj.shape[0] * K().recurrence_record(m, dk, dv),), float("nan"), device=DEV)
+        oraw = torch.full((pj.shape[0], wv), float("nan"), device=DEV)
+        K().recurrence(m, pj, offs, state, out, dev(hb.q_start), dev(hb.slots), prep, oraw, **kw)
         at = 0
         for r, n in take:
             got[r].append(out[at:at + n].float().cpu())
