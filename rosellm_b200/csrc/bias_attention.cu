@@ -16,7 +16,8 @@
 //
 // `bias_attn_kernel`: rows of a block are (token, head) pairs that share a key/value head, so a key tile
 // fetched once serves all of a group's heads; 32 rows x 32 keys a round, online softmax, float32 on the CUDA
-// cores.  A decoded token is a tile of one token.
+// cores.  A decoded token is a tile of one token; where a step has few of them, the keys of each are cut into
+// parts, a block a part, and `bias_attn_merge_kernel` puts the parts together in their order.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -42,6 +43,11 @@ struct BiasAttnParams {
   int temp_every;
   const float* slopes;  // [n_heads] or null
   int* status;
+  // decoded tokens whose keys are cut into parts: a block takes one part and leaves its unnormalised sums
+  // in part_o [(decoded request, head, part), dv] and (maximum, sum of weights) in part_ml
+  int n_splits;
+  float* part_o;
+  float* part_ml;
 };
 
 template <typename T, int DVC, typename TOut>
@@ -50,14 +56,18 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   pdl_begin();
   const int subs = p.tile_tokens / p.tokens_per_block;
   int req, first;  // the request and the first of its new tokens that this block takes
+  int split = 0, dec = -1;  // for a decoded token: which part of its keys, and its place among the decoded requests
   if ((int)blockIdx.x < p.n_tiles * subs) {
     const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
     req = p.tiles[2 * tile];
     first = p.tiles[2 * tile + 1] + sub * p.tokens_per_block;
   } else {
-    req = p.decode_reqs[blockIdx.x - p.n_tiles * subs];
+    dec = (blockIdx.x - p.n_tiles * subs) / p.n_splits;
+    split = (blockIdx.x - p.n_tiles * subs) - dec * p.n_splits;
+    req = p.decode_reqs[dec];
     first = 0;
   }
+  const bool parted = dec >= 0 && p.n_splits > 1;
   const int slot = p.slots[req];
   const int t_begin = p.q_start[req], n_new = p.q_start[req + 1] - t_begin;
   if (slot < 0 || first >= n_new) return;
@@ -126,9 +136,16 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   const bool vec = dk % EV == 0 && dv % EV == 0 && p.row % EV == 0 && p.v_at % EV == 0 &&
                    (reinterpret_cast<uintptr_t>(p.pool) & 15) == 0;
   for (int i = tid; i < BA_KEYS * ldv_s; i += BA_THREADS) Vs[i] = 0.f;  // the fill beyond dv stays zero
-  locate(0, 0);
+  int j_begin = 0, j_end = last_pos + 1;  // the keys this block walks
+  if (parted) {
+    const int tiles_all = (last_pos + BA_KEYS) / BA_KEYS;
+    const int per = (tiles_all + p.n_splits - 1) / p.n_splits;
+    j_begin = split * per * BA_KEYS;
+    j_end = min(j_end, (split + 1) * per * BA_KEYS);
+  }
+  locate(j_begin, 0);
   int buf = 0;
-  for (int j0 = 0; j0 <= last_pos; j0 += BA_KEYS, buf ^= 1) {
+  for (int j0 = j_begin; j0 < j_end; j0 += BA_KEYS, buf ^= 1) {
     __syncthreads();  // the tile before has been used; this tile's places (and, the first time, the queries) are known
     if (vec) {
       const int kp = dk / EV, vp = dv / EV, per_key = kp + vp;
@@ -216,6 +233,21 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
       }
     }
   }
+  if (parted) {
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      if (!row_ok[a]) continue;
+      const size_t at = ((size_t)dec * p.n_heads + row_head[a]) * p.n_splits + split;
+#pragma unroll
+      for (int c = 0; c < DVC; ++c)
+        if (tx + 8 * c < dv) p.part_o[at * dv + tx + 8 * c] = acc[a][c];
+      if (tx == 0) {
+        p.part_ml[2 * at] = m[a];
+        p.part_ml[2 * at + 1] = l[a];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int a = 0; a < 2; ++a) {
     if (!row_ok[a]) continue;
@@ -231,6 +263,39 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
         if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col]));
         o[col] = from_f32<TOut>(v);
       }
+    }
+  }
+}
+
+// The parts of a decoded token's keys put together, in their order: out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
+// times the gate.  A block a decoded request, a warp a head.
+template <typename TOut>
+__global__ __launch_bounds__(128) void bias_attn_merge_kernel(const BiasAttnParams p) {
+  pdl_begin();
+  const int dec = blockIdx.x, req = p.decode_reqs[dec];
+  if (p.slots[req] < 0) return;
+  const int tok = p.q_start[req], dv = p.dv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int head = warp; head < p.n_heads; head += blockDim.x >> 5) {
+    const size_t at = ((size_t)dec * p.n_heads + head) * p.n_splits;
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, p.part_ml[2 * (at + s)]);
+    float L = 0.f;
+    for (int s = 0; s < p.n_splits; ++s) {
+      const float ms = p.part_ml[2 * (at + s)];
+      if (ms != -CUDART_INF_F) L = fmaf(p.part_ml[2 * (at + s) + 1], expf(ms - M), L);
+    }
+    TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
+    const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)head * dv : nullptr;
+    for (int c = lane; c < dv; c += 32) {
+      float acc = 0.f;
+      for (int s = 0; s < p.n_splits; ++s) {
+        const float ms = p.part_ml[2 * (at + s)];
+        if (ms != -CUDART_INF_F) acc = fmaf(p.part_o[(at + s) * dv + c], expf(ms - M), acc);
+      }
+      float v = acc / L;
+      if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[c]));
+      o[c] = from_f32<TOut>(v);
     }
   }
 }
@@ -307,6 +372,8 @@ RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int* heads_per_block,
   return 0;
 }
 
+// n_splits > 1: every decoded request's keys are cut into so many parts, a block each, merged by a second
+// kernel; part_o float32 [n_decode * heads * n_splits, dv], part_ml float32 [n_decode * heads * n_splits, 2].
 // tiles: (request, first new token) of portions cut every `tile_tokens` tokens (a multiple of the tokens a
 // block takes); decode_reqs: the requests that bring one token.  cache_dtype: the pool's element type;
 // out_dtype: that of out.
@@ -315,7 +382,8 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
                                 const int* kv_len, const int* slots, const int* tiles, int n_tiles, int tile_tokens,
                                 const int* decode_reqs, int n_decode, void* out, long ldo, int n_heads, int n_kv, int dk,
                                 int dv, int v_at, int row, int page_size, int max_pages, float scale, float temp_coef,
-                                int temp_every, const float* slopes, int* status, cudaStream_t stream) {
+                                int temp_every, const float* slopes, int* status, int n_splits, float* part_o,
+                                float* part_ml, cudaStream_t stream) {
   if (n_tiles <= 0 && n_decode <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || v_at < dk ||
       v_at + dv > row || n_kv > 65535)
@@ -324,17 +392,23 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   rl_bias_attention_shape(n_heads / n_kv, &hb, &tt);
   if (n_tiles > 0 && (tile_tokens < tt || tile_tokens % tt)) return -3;
   if (n_tiles <= 0) tile_tokens = tt;
+  if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
+  if (n_decode <= 0) n_splits = 1;
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
-                       tt, hb, n_decode > 0 ? n_decode : 0, scale, temp_coef, temp_every, slopes, status};
+                       tt, hb, n_decode > 0 ? n_decode : 0, scale, temp_coef, temp_every, slopes, status, n_splits, part_o, part_ml};
   const int head_blocks = (n_heads / n_kv + hb - 1) / hb;
-  const dim3 grid(p.n_tiles * (tile_tokens / tt) + p.n_decode, n_kv, head_blocks);
+  const dim3 grid(p.n_tiles * (tile_tokens / tt) + p.n_decode * n_splits, n_kv, head_blocks);
   if (cache_dtype == RL_F32) {
     if (out_dtype == RL_F32) rl::dispatch_bias_attn<float, float>(p, grid, stream);
     else rl::dispatch_bias_attn<float, __nv_bfloat16>(p, grid, stream);
   } else {
     if (out_dtype == RL_F32) rl::dispatch_bias_attn<__nv_bfloat16, float>(p, grid, stream);
     else rl::dispatch_bias_attn<__nv_bfloat16, __nv_bfloat16>(p, grid, stream);
+  }
+  if (n_splits > 1) {
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::bias_attn_merge_kernel<float>, p.n_decode, 128, 0, stream, p);
+    else rl::launch_pdl(rl::bias_attn_merge_kernel<__nv_bfloat16>, p.n_decode, 128, 0, stream, p);
   }
   RL_CHECK_LAUNCH();
   return 0;

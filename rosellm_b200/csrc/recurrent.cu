@@ -16,7 +16,8 @@
 //     [w | k | r (| u | a*u)] of DKP entries each, then the token's values (DVP entries);
 //   `recurrence_seq_kernel`, a block a (request, head): the only sequential part.  Four neighbouring lanes share
 //     a column of the state, each holding a quarter of its rows in registers; a token costs them two reductions
-//     over the four lanes (u^T S and S^T r); a block takes up to 64 columns, further blocks the rest.  The records of a chunk of tokens are one contiguous piece of memory,
+//     over the four lanes (u^T S and S^T r); a block takes 8 to 64 columns, further blocks the rest.  The records of a
+//     chunk of tokens are one contiguous piece of memory,
 //     copied into shared memory with cp.async while the chunk before is worked on;
 //   `recurrence_out_kernel`, a warp a (token, head): the head's norm, weight and gate, in the activation type.
 #include "common.cuh"
@@ -45,24 +46,27 @@ struct RecurParams {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// dynamic shared memory: tanh of the low-rank input [rank], k [heads * dk], a [heads * dk] (MODE 0)
+// A block takes one token and `heads_per_block` heads.  Dynamic shared memory (MODE 0): tanh of the low-rank
+// input [rank], then k and a of the block's channels [heads_per_block * dk] each.
 template <int MODE>
-__global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams p) {
+__global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams p, int heads_per_block) {
   extern __shared__ float prep_s[];
   pdl_begin();
   const int tok = blockIdx.x;
+  const int h0 = blockIdx.y * heads_per_block, h1 = min(p.n_heads, h0 + heads_per_block);  // this block's heads
   const int C = p.n_heads * p.dk, dk = p.dk, dkp = p.dkp;
   const float* row = p.proj + (size_t)tok * p.ldp;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   auto record = [&](int head) { return p.prep + ((size_t)head * p.n_tokens + tok) * p.rec; };
   if (MODE == 0) {
     float* Ls = prep_s;
-    float* Ks = Ls + p.rank;
-    float* As = Ks + C;
+    float* Ks = Ls + p.rank - h0 * dk;            // indexed by channel; the block's own channels are kept
+    float* As = Ks + heads_per_block * dk;
     for (int r = threadIdx.x; r < p.rank; r += blockDim.x) Ls[r] = tanhf(row[p.off_w + r]);
     __syncthreads();
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = h0 * dk + threadIdx.x; c < h1 * dk; c += blockDim.x) {
       float wl = p.w0[c];
+#pragma unroll 8
       for (int q = 0; q < p.rank; ++q) wl = fmaf(p.w2t[(size_t)q * C + c], Ls[q], wl);
       const int head = c / dk, i = c - head * dk;
       float* rec = record(head);
@@ -74,7 +78,7 @@ __global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams 
       As[c] = sigmoidf_(row[p.off_a + c] + p.a_bias[c]);
     }
     __syncthreads();
-    for (int head = warp; head < p.n_heads; head += n_warps) {
+    for (int head = h0 + warp; head < h1; head += n_warps) {
       float ss = 0.f;
       for (int i = lane; i < dk; i += 32) ss = fmaf(Ks[head * dk + i], Ks[head * dk + i], ss);
       ss = warp_sum(ss);
@@ -88,7 +92,7 @@ __global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams 
       }
     }
   } else {
-    for (int c = threadIdx.x; c < p.n_heads * dkp; c += blockDim.x) {
+    for (int c = h0 * dkp + threadIdx.x; c < h1 * dkp; c += blockDim.x) {
       const int head = c / dkp, i = c - head * dkp;
       float w = 0.f, k = 0.f, r = 0.f;
       if (i < dk) {
@@ -107,7 +111,7 @@ __global__ __launch_bounds__(256) void recurrence_prep_kernel(const RecurParams 
     }
   }
   constexpr int NV = MODE == 0 ? 5 : 3;
-  for (int c = threadIdx.x; c < p.n_heads * p.dvp; c += blockDim.x) {
+  for (int c = h0 * p.dvp + threadIdx.x; c < h1 * p.dvp; c += blockDim.x) {
     const int head = c / p.dvp, j = c - head * p.dvp;
     record(head)[NV * dkp + j] = j < p.dv ? row[p.off_v + head * p.dv + j] : 0.f;
   }
@@ -126,10 +130,10 @@ __device__ __forceinline__ void cp_async_wait() {
 // DKQ: state rows a thread (a quarter of DKP).  Thread (column = tid / 4, part = tid % 4) holds the rows
 // 16 m + 4 part + e (m < DKQ / 4, e < 4) of its column: the four parts read neighbouring 16-byte pieces
 // of a record's vectors.  chunk: tokens a buffer of shared memory.
-constexpr int REC_COLS = 64;  // state columns a block (four threads each)
+constexpr int REC_COLS = 64;  // most state columns a block (four threads each)
 
 template <int MODE, int DKQ>
-__global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const RecurParams p, int chunk) {
+__global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const RecurParams p, int chunk, int cols) {
   extern __shared__ __align__(16) float seq_s[];
   pdl_begin();
   const int req = blockIdx.x, head = blockIdx.y;
@@ -139,7 +143,7 @@ __global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const Recu
   constexpr int DKP = 4 * DKQ;
   const int t0 = p.q_start[req], t1 = p.q_start[req + 1];
   const int dk = p.dk, dv = p.dv, rec = p.rec;
-  const int col = blockIdx.z * REC_COLS + (threadIdx.x >> 2), part = threadIdx.x & 3;
+  const int col = blockIdx.z * cols + (threadIdx.x >> 2), part = threadIdx.x & 3;
   float S[DKQ];
   float* st = p.state + (((size_t)slot * p.n_heads + head) * dk) * dv;
 #pragma unroll
@@ -257,10 +261,21 @@ static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
       raised = true;
     }
   }
-  const int col_blocks = (p.dv + REC_COLS - 1) / REC_COLS;
-  const int cols = (p.dv + col_blocks - 1) / col_blocks;  // the last block's share may be shorter
-  const int threads = col_blocks == 1 ? (4 * cols + 31) / 32 * 32 : 4 * REC_COLS;
-  launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), threads, smem, stream, p, chunk);
+  // Columns a block: every warp of a block reads the whole record of a token from shared memory, and a
+  // token's work is a chain of dependent steps, so few columns a block and many blocks are what is fast,
+  // as long as there are SMs for them: halved from 64 until the grid fills the device (8 columns: one warp).
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  int cols = (p.dv + 7) / 8 * 8;
+  cols = cols > REC_COLS ? REC_COLS : cols;
+  while (cols > 8 && (long)n_reqs * p.n_heads * ((p.dv + cols - 1) / cols) < sms) cols /= 2;
+  const int col_blocks = (p.dv + cols - 1) / cols;
+  launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), 4 * cols, smem, stream, p, chunk, cols);
 }
 
 template <int MODE>
@@ -302,22 +317,19 @@ RL_EXPORT int rl_recurrence(int mode, int out_dtype, const float* proj, long ldp
   if (rl_recurrence_record(mode, dk, dv, &dkp, &dvp, &rec) != 0 || n_heads <= 0 || n_heads > 65535 || rank < 0) return -2;
   rl::RecurParams p{proj, ldp, off_r, off_k, off_v, off_a, off_g, off_w, a_bias, w0, w2t, rank, out_weight, state, out,
                     ldo, q_start, slots, prep, oraw, n_tokens, n_heads, dk, dv, dkp, dvp, rec, eps, decay_scale, unit_eps};
-  const size_t prep_smem = mode == 0 ? ((size_t)rank + 2 * (size_t)n_heads * dk) * sizeof(float) : 0;
-  if (prep_smem > 160 * 1024) return -2;
+  // heads a block of the preparation: about 256 channels (a thread a channel), fewer with many tokens' worth of blocks anyway
+  int hpb = 256 / dk;
+  hpb = hpb < 1 ? 1 : (hpb > n_heads ? n_heads : hpb);
+  const dim3 prep_grid(n_tokens, (n_heads + hpb - 1) / hpb);
+  const size_t prep_smem = mode == 0 ? ((size_t)rank + 2 * (size_t)hpb * dk) * sizeof(float) : 0;
+  if (prep_smem > 48 * 1024) return -2;
   if (mode == 0) {
-    if (prep_smem > 48 * 1024) {
-      static bool raised = false;
-      if (!raised) {
-        rl::note_launch(cudaFuncSetAttribute(rl::recurrence_prep_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        raised = true;
-      }
-    }
-    rl::launch_pdl(rl::recurrence_prep_kernel<0>, n_tokens, 256, prep_smem, stream, p);
+    rl::launch_pdl(rl::recurrence_prep_kernel<0>, prep_grid, 256, prep_smem, stream, p, hpb);
     rl::dispatch_seq<0>(p, n_reqs, stream);
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<0, float>, n_tokens, 256, 0, stream, p);
     else rl::launch_pdl(rl::recurrence_out_kernel<0, __nv_bfloat16>, n_tokens, 256, 0, stream, p);
   } else {
-    rl::launch_pdl(rl::recurrence_prep_kernel<1>, n_tokens, 256, 0, stream, p);
+    rl::launch_pdl(rl::recurrence_prep_kernel<1>, prep_grid, 256, 0, stream, p, hpb);
     rl::dispatch_seq<1>(p, n_reqs, stream);
     if (out_dtype == RL_F32) rl::launch_pdl(rl::recurrence_out_kernel<1, float>, n_tokens, 256, 0, stream, p);
     else rl::launch_pdl(rl::recurrence_out_kernel<1, __nv_bfloat16>, n_tokens, 256, 0, stream, p);

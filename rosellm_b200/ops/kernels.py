@@ -173,7 +173,7 @@ def _lib() -> ctypes.CDLL:
         lib.rl_recurrence_record.argtypes = [I, I, I, P, P, P]
         lib.rl_bias_attention_shape.argtypes = [I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
-                                          F, F, I, P, P, P]
+                                          F, F, I, P, P, I, P, P, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
@@ -1322,8 +1322,11 @@ def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_
 
 def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, dk: int, dv: int, v_at: int,
                    scale: float, slopes=None, temp_coef: float = 0.0, temp_every: int = 0, tiles=None, n_tiles: int = 0,
-                   tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int) -> None:
+                   tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int, n_splits: int = 1, part_o=None,
+                   part_ml=None) -> None:
     """Causal attention of the step's queries over the cached rows (csrc/bias_attention.cu).
+    ``n_splits`` > 1: the keys of every decoded request are cut into so many parts (``part_o`` float32
+    [n_decode * heads * n_splits, dv] and ``part_ml`` [.., 2] are their scratch) and merged in order.
     ``q`` float32 [tokens, heads * dk] and ``gate`` float32 [tokens, heads * dv] (or ``None``) may be views
     with a row stride; ``out`` [tokens, heads * dv] float32 or bfloat16; ``slopes`` float32 [heads] or ``None``."""
     _need(q, "q", torch.float32, contiguous=False)
@@ -1340,13 +1343,22 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
         _need(slopes, "slopes", torch.float32)
         if slopes.numel() != n_heads:
             raise KernelError("bias_attention: one slope a head")
+    global _launches
+    if n_decode <= 0:
+        n_splits = 1
+    if n_splits > 1:
+        if part_o is None or part_ml is None or part_o.dtype != torch.float32 or part_ml.dtype != torch.float32 \
+                or part_o.numel() < n_decode * n_heads * n_splits * dv or part_ml.numel() < n_decode * n_heads * n_splits * 2:
+            raise KernelError("bias_attention: the parts' scratch is missing or too small")
+        _launches += 1
     rc = _lib().rl_bias_attention(_code(pool), _code(out), _ptr(q), q.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
                                   _ptr(pool), _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len),
                                   _ptr(slots), _ptr(tiles), int(n_tiles), int(tile_tokens), _ptr(decode_reqs), int(n_decode),
                                   _ptr(out), out.stride(0), n_heads, n_kv, dk, dv, int(v_at), row, page_size,
                                   min(block_table.shape[1], -(-max_pos // page_size)), float(scale), float(temp_coef),
-                                  int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), _stream())
-    if rc in (-2, -3):
+                                  int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), int(n_splits), _ptr(part_o),
+                                  _ptr(part_ml), _stream())
+    if rc in (-2, -3, -4):
         raise KernelError(f"bias_attention: sizes not taken (code {rc}: key and value sizes up to 256; tiles a multiple "
                           "of the tokens a block takes)")
     _ok(rc, "bias_attention")

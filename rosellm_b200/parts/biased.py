@@ -62,6 +62,20 @@ class BiasedAttention(Part):
         self.proj_weight = self.out_weight = self.mix_weight = self.slopes = None
         self._shape = None
 
+    def decode_plan_for(self, n_decode: int, span: int, act_dtype=None) -> tuple[int, bool]:
+        """(parts, False): into how many parts the keys of a decoded request are cut when ``n_decode`` requests
+        attend over about ``span`` keys each.  A block walks its keys 32 at a time, one tile after the other,
+        so with few requests the keys are spread over as many blocks as the device has room for, each
+        keeping at least two tiles; the parts are merged in their order by a second kernel."""
+        if n_decode <= 0:
+            return 1, False
+        blocks = n_decode * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 32)
+        tiles = max(1, -(-span // 32))
+        return max(1, min(2 * K.sm_count() // blocks, tiles // 2, 32)), False
+
+    def launch_key(self, ctx) -> tuple:
+        return (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len),) if ctx.n_decode else ()
+
     def param_specs(self):
         hid = self.hidden_size
         specs = [ParamSpec("q_weight", (self.q_width, hid)), ParamSpec("k_weight", (self.k_width, hid)),
@@ -120,10 +134,16 @@ class BiasedAttention(Part):
         if self._shape is None:
             self._shape = K.bias_attention_shape(self.num_heads // self.num_kv_heads)
         wide = self._shape[1] > 16  # the tokens a block takes must divide the tiles the step is cut into
+        splits = (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len))[0]
+        part_o = part_ml = None
+        if splits > 1:
+            rows = ctx.n_decode * self.num_heads * splits
+            part_o = ws.get("biased_attn_part_o", (rows, self.value_dim), torch.float32)
+            part_ml = ws.get("biased_attn_part_ml", (rows, 2), torch.float32)
         K.bias_attention(q, gate, pool, table, ctx.q_start, ctx.kv_len, ctx.slots, out, n_heads=self.num_heads,
                          dk=self.key_dim, dv=self.value_dim, v_at=self.v_at, scale=self.scale, slopes=self.slopes,
                          temp_coef=self.temp_coef, temp_every=self.temp_every,
                          tiles=ctx.tiles_wide if wide else ctx.tiles, n_tiles=ctx.n_tiles_wide if wide else ctx.n_tiles,
                          tile_tokens=64 if wide else 16, decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode,
-                         max_pos=ctx.cache.max_seq_len)
+                         max_pos=ctx.cache.max_seq_len, n_splits=splits, part_o=part_o, part_ml=part_ml)
         K.linear(buf, self.out_weight, None, x, residual=add)

@@ -79,7 +79,7 @@ def test_norm_with_scales_around_zero_and_the_fused_pair(width):
         assert rel(nxt.float(), P.norm(want_x, w2.double(), 1e-3)) < tol
 
 
-def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, seed, stand_out=None, gate=True):
+def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, seed, stand_out=None, gate=True, splits=1):
     """Requests with ``lens_old`` cached tokens bring ``lens_new`` more.  The cache rows of all tokens are
     written by the store kernel (old tokens in a step of their own); returns the kernel's output
     [tokens, H, dv] and the plain result from the same (rounded) keys and values."""
@@ -125,11 +125,15 @@ def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, 
     wide = K().bias_attention_shape(H // G)[1] > 16
     tiles, n_tiles = (hb.tiles_wide, len(hb.tiles_wide)) if wide else (hb.tiles, len(hb.tiles))
     out = torch.full((n_tok, H * dv), 5.0, dtype=dt, device=DEV)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.full((len(hb.decode_reqs) * H * splits, dv), float("nan"), device=DEV)
+        part_ml = torch.full((len(hb.decode_reqs) * H * splits, 2), float("nan"), device=DEV)
     K().bias_attention(q.reshape(n_tok, H * dk).to(DEV), None if gate_t is None else gate_t.to(DEV), pool, table,
                        dev(hb.q_start), dev(hb.kv_len), dev(hb.slots), out, n_heads=H, dk=dk, dv=dv, v_at=v_at, scale=scale,
                        slopes=slopes.to(DEV), temp_coef=temp[0], temp_every=temp[1], tiles=dev(tiles.reshape(-1)),
                        n_tiles=n_tiles, tile_tokens=64 if wide else 16, decode_reqs=dev(hb.decode_reqs),
-                       n_decode=len(hb.decode_reqs), max_pos=max(totals))
+                       n_decode=len(hb.decode_reqs), max_pos=max(totals), n_splits=splits, part_o=part_o, part_ml=part_ml)
     K().check_status(torch.device(DEV))
     want = torch.empty(n_tok, H, dv, dtype=torch.float64)
     t0 = 0
@@ -163,13 +167,25 @@ def test_biased_attention_prompt_portions_and_single_tokens(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("splits", [2, 3, 8, 32])
+def test_decoded_tokens_with_keys_cut_into_parts(dtype, splits):
+    """More parts than a short request has tiles of keys (empty parts), parts that end inside a tile, beside a
+    prompt portion that is not cut."""
+    tol = 2e-5 if dtype == "float32" else 1e-2
+    got, want = _attention_case(dtype, 6, 2, 20, 10, [1, 1, 5, 1, 1], [700, 0, 40, 63, 64], 16, 0.25, (0.7, 16), seed=splits,
+                                splits=splits)
+    assert rel(got, want) < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key", [0, 15, 16, 17, 511, 512, 897])
 def test_a_far_key_that_stands_out_is_found(dtype, key):
     """Among 900 cached keys one is scored far above the rest for the head with the smallest slope: the
     output must be (nearly) that key's value, whether it is the first, sits at a page's border or far
     back; from a prompt portion's query and from a decoded token's."""
-    for new, old in (([4], [896]), ([1], [899])):
-        got, want = _attention_case(dtype, 4, 2, 24, 12, new, old, 16, 0.5, (0.0, 0), seed=key, stand_out=(key, 3), gate=False)
+    for new, old, splits in (([4], [896], 1), ([1], [899], 1), ([1], [899], 5)):
+        got, want = _attention_case(dtype, 4, 2, 24, 12, new, old, 16, 0.5, (0.0, 0), seed=key, stand_out=(key, 3), gate=False,
+                                    splits=splits)
         assert rel(got, want) < (2e-5 if dtype == "float32" else 1e-2)
 
 
