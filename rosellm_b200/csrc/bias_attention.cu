@@ -268,7 +268,7 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
 }
 
 // The parts of a decoded token's keys put together, in their order: out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M),
-// times the gate.  A block a decoded request, a warp a head.
+// times the gate.  A warp a (decoded request, head); lane s works out part s's weight once (at most 32 parts).
 template <typename TOut>
 __global__ __launch_bounds__(128) void bias_attn_merge_kernel(const BiasAttnParams p) {
   pdl_begin();
@@ -276,23 +276,25 @@ __global__ __launch_bounds__(128) void bias_attn_merge_kernel(const BiasAttnPara
   if (p.slots[req] < 0) return;
   const int tok = p.q_start[req], dv = p.dv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int head = warp; head < p.n_heads; head += blockDim.x >> 5) {
-    const size_t at = ((size_t)dec * p.n_heads + head) * p.n_splits;
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, p.part_ml[2 * (at + s)]);
-    float L = 0.f;
+  const int head = blockIdx.y * 4 + warp;
+  if (head >= p.n_heads) return;
+  const size_t at = ((size_t)dec * p.n_heads + head) * p.n_splits;
+  const float ms = lane < p.n_splits ? p.part_ml[2 * (at + lane)] : -CUDART_INF_F;
+  const float ls = lane < p.n_splits ? p.part_ml[2 * (at + lane) + 1] : 0.f;
+  const float M = warp_max(ms);
+  const float w = ms == -CUDART_INF_F ? 0.f : expf(ms - M);
+  float L = 0.f;  // summed in the parts' order, by every lane alike
+  for (int s = 0; s < p.n_splits; ++s) L = fmaf(__shfl_sync(0xffffffffu, ls, s), __shfl_sync(0xffffffffu, w, s), L);
+  TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
+  const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)head * dv : nullptr;
+  for (int c0 = 0; c0 < dv; c0 += 32) {
+    const int c = c0 + lane;
+    float acc = 0.f;
     for (int s = 0; s < p.n_splits; ++s) {
-      const float ms = p.part_ml[2 * (at + s)];
-      if (ms != -CUDART_INF_F) L = fmaf(p.part_ml[2 * (at + s) + 1], expf(ms - M), L);
+      const float ws = __shfl_sync(0xffffffffu, w, s);
+      if (c < dv && ws != 0.f) acc = fmaf(p.part_o[(at + s) * dv + c], ws, acc);
     }
-    TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)head * dv;
-    const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)head * dv : nullptr;
-    for (int c = lane; c < dv; c += 32) {
-      float acc = 0.f;
-      for (int s = 0; s < p.n_splits; ++s) {
-        const float ms = p.part_ml[2 * (at + s)];
-        if (ms != -CUDART_INF_F) acc = fmaf(p.part_o[(at + s) * dv + c], expf(ms - M), acc);
-      }
+    if (c < dv) {
       float v = acc / L;
       if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[c]));
       o[c] = from_f32<TOut>(v);
@@ -392,7 +394,7 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   rl_bias_attention_shape(n_heads / n_kv, &hb, &tt);
   if (n_tiles > 0 && (tile_tokens < tt || tile_tokens % tt)) return -3;
   if (n_tiles <= 0) tile_tokens = tt;
-  if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
+  if (n_splits < 1 || n_splits > 32 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
   if (n_decode <= 0) n_splits = 1;
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
@@ -407,8 +409,9 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
     else rl::dispatch_bias_attn<__nv_bfloat16, __nv_bfloat16>(p, grid, stream);
   }
   if (n_splits > 1) {
-    if (out_dtype == RL_F32) rl::launch_pdl(rl::bias_attn_merge_kernel<float>, p.n_decode, 128, 0, stream, p);
-    else rl::launch_pdl(rl::bias_attn_merge_kernel<__nv_bfloat16>, p.n_decode, 128, 0, stream, p);
+    const dim3 mg(p.n_decode, (n_heads + 3) / 4);
+    if (out_dtype == RL_F32) rl::launch_pdl(rl::bias_attn_merge_kernel<float>, mg, 128, 0, stream, p);
+    else rl::launch_pdl(rl::bias_attn_merge_kernel<__nv_bfloat16>, mg, 128, 0, stream, p);
   }
   RL_CHECK_LAUNCH();
   return 0;

@@ -14,11 +14,10 @@
 //   `recurrence_prep_kernel`, a block a token: everything that does not depend on the state (sigmoids,
 //     exponentials, the low-rank product, the unit key), in float32, into one record per (head, token):
 //     [w | k | r (| u | a*u)] of DKP entries each, then the token's values (DVP entries);
-//   `recurrence_seq_kernel`, a block a (request, head): the only sequential part.  Four neighbouring lanes share
-//     a column of the state, each holding a quarter of its rows in registers; a token costs them two reductions
-//     over the four lanes (u^T S and S^T r); a block takes 8 to 64 columns, further blocks the rest.  The records of a
-//     chunk of tokens are one contiguous piece of memory,
-//     copied into shared memory with cp.async while the chunk before is worked on;
+//   `recurrence_seq_kernel`, a block a (request, head, group of state columns): the only sequential part.  Eight
+//     neighbouring lanes share a column of the state, each holding an eighth of its rows in registers; a token costs
+//     them two reductions over the eight lanes (u^T S and S^T r).  The records of a chunk of tokens are one contiguous
+//     piece of memory, copied into shared memory with cp.async while the chunk before is worked on;
 //   `recurrence_out_kernel`, a warp a (token, head): the head's norm, weight and gate, in the activation type.
 #include "common.cuh"
 
@@ -127,40 +126,62 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// DKQ: state rows a thread (a quarter of DKP).  Thread (column = tid / 4, part = tid % 4) holds the rows
-// 16 m + 4 part + e (m < DKQ / 4, e < 4) of its column: the four parts read neighbouring 16-byte pieces
-// of a record's vectors.  chunk: tokens a buffer of shared memory.
-constexpr int REC_COLS = 64;  // most state columns a block (four threads each)
+// TPC lanes share a column of the state; DKQ = DKP / TPC rows a thread.  Thread (column = tid / TPC, part =
+// tid % TPC) holds the rows 4 TPC m + 4 part + e (m < DKQ / 4, e < 4) of its column: the parts read
+// neighbouring 16-byte pieces of a record's vectors.  chunk: tokens a buffer of shared memory; cols: columns a
+// block.  A token is a chain of dependent steps (u^T S, its reduction over the parts, the update, S^T r, its
+// reduction), and a warp has nothing else to do meanwhile: so the vectors of the NEXT token are taken from
+// shared memory into registers before the current token's reductions, and the chain itself is kept short.
+constexpr int REC_THREADS = 256;  // most threads a block
 
-template <int MODE, int DKQ>
-__global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const RecurParams p, int chunk, int cols) {
+template <int MODE, int NV, int DKQ>
+struct TokenVectors {
+  float4 v[NV][DKQ / 4];
+  float value;
+};
+
+template <int MODE, int TPC, int DKQ>
+__global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const RecurParams p, int chunk, int cols) {
   extern __shared__ __align__(16) float seq_s[];
   pdl_begin();
   const int req = blockIdx.x, head = blockIdx.y;
   const int slot = p.slots[req];
   if (slot < 0) return;  // a padding row of a captured step
   constexpr int NV = MODE == 0 ? 5 : 3;
-  constexpr int DKP = 4 * DKQ;
+  constexpr int DKP = TPC * DKQ;
   const int t0 = p.q_start[req], t1 = p.q_start[req + 1];
   const int dk = p.dk, dv = p.dv, rec = p.rec;
-  const int col = blockIdx.z * cols + (threadIdx.x >> 2), part = threadIdx.x & 3;
+  const int col = blockIdx.z * cols + threadIdx.x / TPC, part = threadIdx.x % TPC;
   float S[DKQ];
   float* st = p.state + (((size_t)slot * p.n_heads + head) * dk) * dv;
 #pragma unroll
   for (int k = 0; k < DKQ; ++k) {
-    const int r = (k >> 2) * 16 + 4 * part + (k & 3);
+    const int r = (k >> 2) * 4 * TPC + 4 * part + (k & 3);
     S[k] = (r < dk && col < dv) ? st[(size_t)r * dv + col] : 0.f;
   }
   const float* src = p.prep + ((size_t)head * p.n_tokens + t0) * rec;
-  const int n_chunks = (t1 - t0 + chunk - 1) / chunk;
+  const int n_tok = t1 - t0;
+  const int n_chunks = (n_tok + chunk - 1) / chunk;
   auto fetch = [&](int c) {
-    const int nt = min(chunk, t1 - t0 - c * chunk);
+    const int nt = min(chunk, n_tok - c * chunk);
     float* dst = seq_s + (size_t)(c & 1) * chunk * rec;
     const float* from = src + (size_t)c * chunk * rec;
     for (int i = threadIdx.x; i < nt * rec / 4; i += blockDim.x) cp_async16(dst + 4 * i, from + 4 * i);
     cp_async_commit();
   };
+  auto take = [&](const float* r_, auto& tv) {
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const float4* V4 = reinterpret_cast<const float4*>(r_ + n * DKP);
+#pragma unroll
+      for (int m = 0; m < DKQ / 4; ++m) tv.v[n][m] = V4[TPC * m + part];
+    }
+    tv.value = col < p.dvp ? r_[NV * DKP + col] : 0.f;
+  };
   fetch(0);
+  constexpr bool AHEAD = NV * DKQ <= 80;  // two sets of a token's vectors fit the registers
+  TokenVectors<MODE, NV, DKQ> cur;
+  TokenVectors<MODE, NV, AHEAD ? DKQ : 4> nxt;
   for (int c = 0; c < n_chunks; ++c) {
     if (c + 1 < n_chunks) {
       fetch(c + 1);
@@ -169,35 +190,33 @@ __global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const Recu
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int nt = min(chunk, t1 - t0 - c * chunk);
+    const int nt = min(chunk, n_tok - c * chunk);
     const float* buf = seq_s + (size_t)(c & 1) * chunk * rec;
+    take(buf, cur);
     for (int t = 0; t < nt; ++t) {
-      const float* r_ = buf + (size_t)t * rec;
-      const float4* W4 = reinterpret_cast<const float4*>(r_);
-      const float4* K4 = reinterpret_cast<const float4*>(r_ + DKP);
-      const float4* R4 = reinterpret_cast<const float4*>(r_ + 2 * DKP);
-      const float4* U4 = reinterpret_cast<const float4*>(r_ + 3 * DKP);
-      const float4* AU4 = reinterpret_cast<const float4*>(r_ + 4 * DKP);
-      const float vj = col < p.dvp ? r_[NV * DKP + col] : 0.f;
+      if constexpr (AHEAD) {
+        if (t + 1 < nt) take(buf + (size_t)(t + 1) * rec, nxt);
+      }
+      const float vj = cur.value;
       float pj = 0.f;
       if (MODE == 0) {
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int m = 0; m < DKQ / 4; ++m) {
-          const float4 u = U4[4 * m + part];
+          const float4 u = cur.v[3][m];
           a0 = fmaf(u.x, S[4 * m], fmaf(u.y, S[4 * m + 1], a0));
           a1 = fmaf(u.z, S[4 * m + 2], fmaf(u.w, S[4 * m + 3], a1));
         }
         pj = a0 + a1;
-        pj += __shfl_xor_sync(0xffffffffu, pj, 1);
-        pj += __shfl_xor_sync(0xffffffffu, pj, 2);
+#pragma unroll
+        for (int o = 1; o < TPC; o <<= 1) pj += __shfl_xor_sync(0xffffffffu, pj, o);
       }
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
       for (int m = 0; m < DKQ / 4; ++m) {
-        const float4 w = W4[4 * m + part], k = K4[4 * m + part], r = R4[4 * m + part];
+        const float4 w = cur.v[0][m], k = cur.v[1][m], r = cur.v[2][m];
         float4 au = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (MODE == 0) au = AU4[4 * m + part];
+        if (MODE == 0) au = cur.v[NV - 1][m];
         const float s0 = fmaf(w.x, S[4 * m], fmaf(-au.x, pj, k.x * vj));
         const float s1 = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, pj, k.y * vj));
         const float s2 = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, pj, k.z * vj));
@@ -210,15 +229,20 @@ __global__ __launch_bounds__(4 * REC_COLS) void recurrence_seq_kernel(const Recu
         o1 = fmaf(s2, r.z, fmaf(s3, r.w, o1));
       }
       float o = o0 + o1;
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+      for (int x = 1; x < TPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
       if (part == 0 && col < dv) p.oraw[(size_t)(t0 + c * chunk + t) * p.n_heads * dv + (size_t)head * dv + col] = o;
+      if constexpr (AHEAD) {
+        cur = nxt;
+      } else {
+        if (t + 1 < nt) take(buf + (size_t)(t + 1) * rec, cur);
+      }
     }
     __syncthreads();  // the buffer is free for the chunk after the next
   }
 #pragma unroll
   for (int k = 0; k < DKQ; ++k) {
-    const int r = (k >> 2) * 16 + 4 * part + (k & 3);
+    const int r = (k >> 2) * 4 * TPC + 4 * part + (k & 3);
     if (r < dk && col < dv) st[(size_t)r * dv + col] = S[k];
   }
 }
@@ -247,13 +271,13 @@ __global__ __launch_bounds__(256) void recurrence_out_kernel(const RecurParams p
   }
 }
 
-template <int MODE, int DKQ>
+template <int MODE, int TPC, int DKQ>
 static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
   // tokens a buffer: as many as two buffers of about 48 KB hold, at most 16
   int chunk = (int)(48 * 1024 / ((size_t)p.rec * sizeof(float)));
   chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
   const size_t smem = (size_t)2 * chunk * p.rec * sizeof(float);
-  auto kernel = recurrence_seq_kernel<MODE, DKQ>;
+  auto kernel = recurrence_seq_kernel<MODE, TPC, DKQ>;
   if (smem > 48 * 1024) {
     static bool raised = false;
     if (!raised) {
@@ -261,9 +285,9 @@ static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
       raised = true;
     }
   }
-  // Columns a block: every warp of a block reads the whole record of a token from shared memory, and a
-  // token's work is a chain of dependent steps, so few columns a block and many blocks are what is fast,
-  // as long as there are SMs for them: halved from 64 until the grid fills the device (8 columns: one warp).
+  // Columns a block: a token's work is a chain of dependent steps that every warp walks for itself, so few
+  // columns a block and many blocks are what is fast, as long as there are SMs for them: halved from the
+  // most a block takes until the grid fills the device (down to one warp).
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -271,21 +295,24 @@ static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
   }
-  int cols = (p.dv + 7) / 8 * 8;
-  cols = cols > REC_COLS ? REC_COLS : cols;
-  while (cols > 8 && (long)n_reqs * p.n_heads * ((p.dv + cols - 1) / cols) < sms) cols /= 2;
+  constexpr int per_warp = 32 / TPC;
+  int cols = (p.dv + per_warp - 1) / per_warp * per_warp;
+  cols = cols > REC_THREADS / TPC ? REC_THREADS / TPC : cols;
+  while (cols > per_warp && (long)n_reqs * p.n_heads * ((p.dv + cols - 1) / cols) < sms) cols /= 2;
+  cols = (cols + per_warp - 1) / per_warp * per_warp;
   const int col_blocks = (p.dv + cols - 1) / cols;
-  launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), 4 * cols, smem, stream, p, chunk, cols);
+  launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), TPC * cols, smem, stream, p, chunk, cols);
 }
 
+// Eight lanes a column wherever a thread still holds whole 16-byte pieces (DKP >= 32); four for DKP = 16.
 template <int MODE>
 static void dispatch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
   switch (p.dkp) {
-    case 16: launch_seq<MODE, 4>(p, n_reqs, stream); break;
-    case 32: launch_seq<MODE, 8>(p, n_reqs, stream); break;
-    case 64: launch_seq<MODE, 16>(p, n_reqs, stream); break;
-    case 128: launch_seq<MODE, 32>(p, n_reqs, stream); break;
-    default: launch_seq<MODE, 64>(p, n_reqs, stream); break;
+    case 16: launch_seq<MODE, 4, 4>(p, n_reqs, stream); break;
+    case 32: launch_seq<MODE, 8, 4>(p, n_reqs, stream); break;
+    case 64: launch_seq<MODE, 8, 8>(p, n_reqs, stream); break;
+    case 128: launch_seq<MODE, 8, 16>(p, n_reqs, stream); break;
+    default: launch_seq<MODE, 8, 32>(p, n_reqs, stream); break;
   }
 }
 
