@@ -235,7 +235,7 @@ class CacheManager:
     # ---- numbers -------------------------------------------------------------
     @property
     def num_free_pages(self) -> int:
-        return min(g.allocator.num_free for g in self.groups) if self.groups else 0
+        return min(g.allocator.num_free for g in self.groups) if self.groups else self.num_pages  # no group: nothing to run out of
 
     @property
     def num_free_slots(self) -> int:

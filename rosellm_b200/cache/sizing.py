@@ -97,6 +97,10 @@ def plan_cache(*, page_size: int, max_num_seqs: int, max_model_len: int, bytes_p
         if kv_cache_tokens <= 0:
             raise ValueError("kv_cache_tokens must be positive")
         return CachePlan(-(-int(kv_cache_tokens) // page_size), max_model_len, "kv_cache_tokens")
+    if bytes_per_token <= 0:
+        # no part caches keys or values (a model of state mixers only): pages bound nothing, and a size
+        # derived from memory has nothing to divide by
+        return CachePlan(max_num_seqs * (-(-max_model_len // page_size)), max_model_len, "max_num_seqs * max_model_len")
     if kv_cache_mem_fraction is None and gpu_memory_utilization is None:
         return CachePlan(-(-max_num_seqs * max_model_len // page_size), max_model_len, "max_num_seqs * max_model_len")
     if mem_get_info is None:

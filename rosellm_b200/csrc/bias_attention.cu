@@ -24,7 +24,7 @@
 
 namespace rl {
 
-constexpr int BA_ROWS = 32, BA_KEYS = 32, BA_THREADS = 128;
+constexpr int BA_ROWS = 32, BA_KEYS = 32, BA_THREADS = 128;  // BA_ROWS: the rows of a prompt tile's block
 
 struct BiasAttnParams {
   const float* q;  // [tokens, ldq]; head h at columns [h * dk, (h + 1) * dk)
@@ -50,8 +50,12 @@ struct BiasAttnParams {
   float* part_ml;
 };
 
-template <typename T, int DVC, typename TOut>
+// LPR lanes share a row (their keys tx + LPR b, their value columns tx + LPR c), RPT rows a thread: a block has
+// (BA_THREADS / LPR) * RPT rows.  Prompt tiles run 8 lanes x 2 rows (32 rows); a decoded token has only its
+// group's heads as rows, so its blocks run 16 or 32 lanes a row (8 or 4 rows) and every thread has work.
+template <typename T, int LPR, int RPT, int DVC, typename TOut>
 __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnParams p) {
+  constexpr int ROWS = BA_THREADS / LPR * RPT, KPT = BA_KEYS / LPR;
   extern __shared__ __align__(16) float ba_s[];
   pdl_begin();
   const int subs = p.tile_tokens / p.tokens_per_block;
@@ -77,27 +81,27 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
   const int hb0 = blockIdx.z * p.heads_per_block;
   const int HB = p.heads_per_block;
   const int dk = p.dk, dv = p.dv;
-  const int ldq_s = dk | 1, ldk_s = dk | 1, ldv_s = 8 * DVC;
-  float* Qs = ba_s;                        // [BA_ROWS][ldq_s]
-  float* Ks = Qs + BA_ROWS * ldq_s;        // [BA_KEYS][ldk_s]
+  const int ldq_s = dk | 1, ldk_s = dk | 1, ldv_s = LPR * DVC;
+  float* Qs = ba_s;                        // [ROWS][ldq_s]
+  float* Ks = Qs + ROWS * ldq_s;           // [BA_KEYS][ldk_s]
   float* Vs = Ks + BA_KEYS * ldk_s;        // [BA_KEYS][ldv_s]
-  float* Ps = Vs + BA_KEYS * ldv_s;        // [BA_ROWS][BA_KEYS + 1]
+  float* Ps = Vs + BA_KEYS * ldv_s;        // [ROWS][BA_KEYS + 1]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int ty = tid >> 3, tx = tid & 7;
+  const int ty = tid / LPR, tx = tid % LPR;
   // queries
-  for (int r = warp; r < BA_ROWS; r += BA_THREADS / 32) {
+  for (int r = warp; r < ROWS; r += BA_THREADS / 32) {
     const int tl = r / HB, hl = r - tl * HB;
     const bool ok = tl < n_tok && hb0 + hl < hg;
     const float* src = p.q + (size_t)(t_begin + first + tl) * p.ldq + (size_t)(g * hg + hb0 + hl) * dk;
     for (int d = lane; d < dk; d += 32) Qs[r * ldq_s + d] = ok ? src[d] : 0.f;
   }
-  int row_pos[2], row_head[2];
-  float row_mul[2], row_slope[2], m[2], l[2];
-  bool row_ok[2];
-  float acc[2][DVC];
+  int row_pos[RPT], row_head[RPT];
+  float row_mul[RPT], row_slope[RPT], m[RPT], l[RPT];
+  bool row_ok[RPT];
+  float acc[RPT][DVC];
 #pragma unroll
-  for (int a = 0; a < 2; ++a) {
-    const int r = ty * 2 + a, tl = r / HB, hl = r - tl * HB;
+  for (int a = 0; a < RPT; ++a) {
+    const int r = ty * RPT + a, tl = r / HB, hl = r - tl * HB;
     row_ok[a] = tl < n_tok && hb0 + hl < hg;
     row_pos[a] = pos0 + tl;
     row_head[a] = g * hg + hb0 + hl;
@@ -176,71 +180,73 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
     }
     locate(j0 + BA_KEYS, buf ^ 1);
     __syncthreads();
-    float s[2][4] = {};
-    const float* q0 = Qs + (ty * 2) * ldq_s;
-    const float* q1 = q0 + ldq_s;
+    float s[RPT][KPT] = {};
+    const float* q0 = Qs + (ty * RPT) * ldq_s;
     const float* kb = Ks + tx * ldk_s;
 #pragma unroll 4
     for (int d = 0; d < dk; ++d) {
-      const float a0 = q0[d], a1 = q1[d];
+      float qa[RPT];
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const float kv = kb[b * 8 * ldk_s + d];
-        s[0][b] = fmaf(a0, kv, s[0][b]);
-        s[1][b] = fmaf(a1, kv, s[1][b]);
+      for (int a = 0; a < RPT; ++a) qa[a] = q0[a * ldq_s + d];
+#pragma unroll
+      for (int b = 0; b < KPT; ++b) {
+        const float kv = kb[b * LPR * ldk_s + d];
+#pragma unroll
+        for (int a = 0; a < RPT; ++a) s[a][b] = fmaf(qa[a], kv, s[a][b]);
       }
     }
 #pragma unroll
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < RPT; ++a) {
       float tile_max = -CUDART_INF_F;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const int j = j0 + tx + 8 * b;
+      for (int b = 0; b < KPT; ++b) {
+        const int j = j0 + tx + LPR * b;
         const bool see = row_ok[a] && j <= row_pos[a];
         s[a][b] = see ? s[a][b] * row_mul[a] - row_slope[a] * (float)(row_pos[a] - j) : -CUDART_INF_F;
         tile_max = fmaxf(tile_max, s[a][b]);
       }
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
+      for (int o = 1; o < LPR; o <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
       const float m_new = fmaxf(m[a], tile_max);
       const float corr = m[a] == -CUDART_INF_F ? 0.f : expf(m[a] - m_new);
       float sum = 0.f;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < KPT; ++b) {
         const float pr = s[a][b] == -CUDART_INF_F ? 0.f : expf(s[a][b] - m_new);
-        Ps[(ty * 2 + a) * (BA_KEYS + 1) + tx + 8 * b] = pr;
+        Ps[(ty * RPT + a) * (BA_KEYS + 1) + tx + LPR * b] = pr;
         sum += pr;
       }
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       l[a] = l[a] * corr + sum;
       m[a] = m_new;
 #pragma unroll
       for (int c = 0; c < DVC; ++c) acc[a][c] *= corr;
     }
-    __syncwarp();  // a row's probabilities are written and read by the eight threads of one warp
-    const float* p0 = Ps + (ty * 2) * (BA_KEYS + 1);
-    const float* p1 = p0 + (BA_KEYS + 1);
+    __syncwarp();  // a row's probabilities are written and read by the lanes of one warp
+    const float* p0 = Ps + (ty * RPT) * (BA_KEYS + 1);
 #pragma unroll 4
     for (int jj = 0; jj < BA_KEYS; ++jj) {
-      const float w0 = p0[jj], w1 = p1[jj];
+      float w[RPT];
+#pragma unroll
+      for (int a = 0; a < RPT; ++a) w[a] = p0[a * (BA_KEYS + 1) + jj];
       const float* vr = Vs + jj * ldv_s + tx;
 #pragma unroll
       for (int c = 0; c < DVC; ++c) {
-        const float v = vr[8 * c];
-        acc[0][c] = fmaf(w0, v, acc[0][c]);
-        acc[1][c] = fmaf(w1, v, acc[1][c]);
+        const float v = vr[LPR * c];
+#pragma unroll
+        for (int a = 0; a < RPT; ++a) acc[a][c] = fmaf(w[a], v, acc[a][c]);
       }
     }
   }
   if (parted) {
 #pragma unroll
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < RPT; ++a) {
       if (!row_ok[a]) continue;
       const size_t at = ((size_t)dec * p.n_heads + row_head[a]) * p.n_splits + split;
 #pragma unroll
       for (int c = 0; c < DVC; ++c)
-        if (tx + 8 * c < dv) p.part_o[at * dv + tx + 8 * c] = acc[a][c];
+        if (tx + LPR * c < dv) p.part_o[at * dv + tx + LPR * c] = acc[a][c];
       if (tx == 0) {
         p.part_ml[2 * at] = m[a];
         p.part_ml[2 * at + 1] = l[a];
@@ -249,15 +255,15 @@ __global__ __launch_bounds__(BA_THREADS) void bias_attn_kernel(const BiasAttnPar
     return;
   }
 #pragma unroll
-  for (int a = 0; a < 2; ++a) {
+  for (int a = 0; a < RPT; ++a) {
     if (!row_ok[a]) continue;
-    const int tok = t_begin + first + (ty * 2 + a) / HB;
+    const int tok = t_begin + first + (ty * RPT + a) / HB;
     const float inv = 1.0f / l[a];
     TOut* o = reinterpret_cast<TOut*>(p.out) + (size_t)tok * p.ldo + (size_t)row_head[a] * dv;
     const float* gr = p.gate != nullptr ? p.gate + (size_t)tok * p.ldg + (size_t)row_head[a] * dv : nullptr;
 #pragma unroll
     for (int c = 0; c < DVC; ++c) {
-      const int col = tx + 8 * c;
+      const int col = tx + LPR * c;
       if (col < dv) {
         float v = acc[a][c] * inv;
         if (gr != nullptr) v *= 1.0f / (1.0f + expf(-gr[col]));
@@ -337,11 +343,12 @@ __global__ void bias_kv_store_kernel(const float* __restrict__ k, long ldk, cons
   }
 }
 
-template <typename T, int DVC, typename TOut>
+template <typename T, int LPR, int RPT, int DVC, typename TOut>
 static void launch_bias_attn(const BiasAttnParams& p, dim3 grid, cudaStream_t stream) {
-  const size_t smem = ((size_t)BA_ROWS * (p.dk | 1) + (size_t)BA_KEYS * (p.dk | 1) + (size_t)BA_KEYS * 8 * DVC +
-                       (size_t)BA_ROWS * (BA_KEYS + 1)) * sizeof(float);
-  auto kernel = bias_attn_kernel<T, DVC, TOut>;
+  constexpr int ROWS = BA_THREADS / LPR * RPT;
+  const size_t smem = ((size_t)ROWS * (p.dk | 1) + (size_t)BA_KEYS * (p.dk | 1) + (size_t)BA_KEYS * LPR * DVC +
+                       (size_t)ROWS * (BA_KEYS + 1)) * sizeof(float);
+  auto kernel = bias_attn_kernel<T, LPR, RPT, DVC, TOut>;
   if (smem > 48 * 1024) {
     static bool raised = false;
     if (!raised) {
@@ -352,12 +359,32 @@ static void launch_bias_attn(const BiasAttnParams& p, dim3 grid, cudaStream_t st
   launch_pdl(kernel, grid, BA_THREADS, smem, stream, p);
 }
 
+// rows: 32 (prompt tiles, and decoded tokens of large groups), 8 or 4 (decoded tokens)
 template <typename T, typename TOut>
-static void dispatch_bias_attn(const BiasAttnParams& p, dim3 grid, cudaStream_t stream) {
-  if (p.dv <= 32) launch_bias_attn<T, 4, TOut>(p, grid, stream);
-  else if (p.dv <= 64) launch_bias_attn<T, 8, TOut>(p, grid, stream);
-  else if (p.dv <= 128) launch_bias_attn<T, 16, TOut>(p, grid, stream);
-  else launch_bias_attn<T, 32, TOut>(p, grid, stream);
+static void dispatch_bias_attn(const BiasAttnParams& p, int rows, dim3 grid, cudaStream_t stream) {
+  if (rows == 4) {
+    if (p.dv <= 64) launch_bias_attn<T, 32, 1, 2, TOut>(p, grid, stream);
+    else launch_bias_attn<T, 32, 1, 8, TOut>(p, grid, stream);
+  } else if (rows == 8) {
+    if (p.dv <= 64) launch_bias_attn<T, 16, 1, 4, TOut>(p, grid, stream);
+    else launch_bias_attn<T, 16, 1, 16, TOut>(p, grid, stream);
+  } else {
+    if (p.dv <= 32) launch_bias_attn<T, 8, 2, 4, TOut>(p, grid, stream);
+    else if (p.dv <= 64) launch_bias_attn<T, 8, 2, 8, TOut>(p, grid, stream);
+    else if (p.dv <= 128) launch_bias_attn<T, 8, 2, 16, TOut>(p, grid, stream);
+    else launch_bias_attn<T, 8, 2, 32, TOut>(p, grid, stream);
+  }
+}
+
+static void dispatch_bias_attn_types(int cache_dtype, int out_dtype, const BiasAttnParams& p, int rows, dim3 grid,
+                                     cudaStream_t stream) {
+  if (cache_dtype == RL_F32) {
+    if (out_dtype == RL_F32) dispatch_bias_attn<float, float>(p, rows, grid, stream);
+    else dispatch_bias_attn<float, __nv_bfloat16>(p, rows, grid, stream);
+  } else {
+    if (out_dtype == RL_F32) dispatch_bias_attn<__nv_bfloat16, float>(p, rows, grid, stream);
+    else dispatch_bias_attn<__nv_bfloat16, __nv_bfloat16>(p, rows, grid, stream);
+  }
 }
 
 }  // namespace rl
@@ -396,17 +423,22 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   if (n_tiles <= 0) tile_tokens = tt;
   if (n_splits < 1 || n_splits > 32 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
   if (n_decode <= 0) n_splits = 1;
+  const int hg = n_heads / n_kv;
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
-                       tt, hb, n_decode > 0 ? n_decode : 0, scale, temp_coef, temp_every, slopes, status, n_splits, part_o, part_ml};
-  const int head_blocks = (n_heads / n_kv + hb - 1) / hb;
-  const dim3 grid(p.n_tiles * (tile_tokens / tt) + p.n_decode * n_splits, n_kv, head_blocks);
-  if (cache_dtype == RL_F32) {
-    if (out_dtype == RL_F32) rl::dispatch_bias_attn<float, float>(p, grid, stream);
-    else rl::dispatch_bias_attn<float, __nv_bfloat16>(p, grid, stream);
-  } else {
-    if (out_dtype == RL_F32) rl::dispatch_bias_attn<__nv_bfloat16, float>(p, grid, stream);
-    else rl::dispatch_bias_attn<__nv_bfloat16, __nv_bfloat16>(p, grid, stream);
+                       tt, hb, 0, scale, temp_coef, temp_every, slopes, status, 1, part_o, part_ml};
+  if (p.n_tiles > 0)  // the prompt portions: 32 rows a block, cut into tokens and heads as rl_bias_attention_shape says
+    rl::dispatch_bias_attn_types(cache_dtype, out_dtype, p, 32, dim3(p.n_tiles * (tile_tokens / tt), n_kv, (hg + hb - 1) / hb),
+                                 stream);
+  if (n_decode > 0) {  // the decoded tokens: a block's rows are heads of one group, 4, 8 or 32 of them
+    const int rows = hg <= 4 ? 4 : (hg <= 8 ? 8 : 32);
+    p.n_tiles = 0;
+    p.n_decode = n_decode;
+    p.n_splits = n_splits;
+    p.tokens_per_block = p.tile_tokens = 1;
+    p.heads_per_block = hg < rows ? hg : rows;
+    rl::dispatch_bias_attn_types(cache_dtype, out_dtype, p, rows,
+                                 dim3(n_decode * n_splits, n_kv, (hg + p.heads_per_block - 1) / p.heads_per_block), stream);
   }
   if (n_splits > 1) {
     const dim3 mg(p.n_decode, (n_heads + 3) / 4);

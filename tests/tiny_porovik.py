@@ -75,11 +75,23 @@ RAW_D = model(2000, 384, 1024, 1e-5, (1499, 1031, 17), [
     (delta(3, 96, 8), None),
     (gated(2, 32, 136), moe(64, 16, 4)),
 ])
+# No attention at all (no cache of keys: state slots only), and attention only, with seven heads on seven
+# key/value heads of odd sizes.
+RAW_E = model(90, 40, 600, 1e-5, (64, 5, 9), [
+    (gated(5, 8, 8), moe(8, 4, 2)),
+    (delta(2, 20, 6), dense(16)),
+])
+RAW_F = model(64, 56, 600, 1e-5, (61, 1, 0), [
+    (attn(7, 7, 9, 5, 0.33, temp=(2.0, 3)), None),
+    (attn(8, 1, 6, 11, 0.4, v_mix=True), dense(40)),
+])
 TINY = {
     "A": dict(raw=RAW_A, seed=21, std=0.2, page_size=16),
     "B": dict(raw=RAW_B, seed=22, std=0.15, page_size=8),
     "C": dict(raw=RAW_C, seed=23, std=0.25, page_size=32),
     "D": dict(raw=RAW_D, seed=24, std=0.07, page_size=16),
+    "E": dict(raw=RAW_E, seed=25, std=0.3, page_size=16),
+    "F": dict(raw=RAW_F, seed=26, std=0.3, page_size=8),
 }
 
 
