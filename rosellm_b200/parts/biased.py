@@ -65,13 +65,14 @@ class BiasedAttention(Part):
     def decode_plan_for(self, n_decode: int, span: int, act_dtype=None) -> tuple[int, bool]:
         """(parts, False): into how many parts the keys of a decoded request are cut when ``n_decode`` requests
         attend over about ``span`` keys each.  A block walks its keys 32 at a time, one tile after the other,
-        so with few requests the keys are spread over as many blocks as the device has room for, each
+        and a tile is a chain of dependent steps, so what hides its latency is other blocks on the same SM
+        (they are small: eight fit): the keys are spread until there are about eight blocks an SM, each
         keeping at least two tiles; the parts are merged in their order by a second kernel."""
         if n_decode <= 0:
             return 1, False
         blocks = n_decode * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 32)
         tiles = max(1, -(-span // 32))
-        return max(1, min(2 * K.sm_count() // blocks, tiles // 2, 32)), False
+        return max(1, min(8 * K.sm_count() // blocks, tiles // 2, 32)), False
 
     def launch_key(self, ctx) -> tuple:
         return (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len),) if ctx.n_decode else ()
