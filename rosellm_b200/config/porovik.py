@@ -8,7 +8,7 @@ the mixer's sizes and constants under ``mixer`` and the feed-forward under ``mlp
 
 Mixer keys: ``attention``: ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``q_temp`` (``coef``,
 ``every``; absent or null: no query temperature), ``v_mix`` (whether the layer takes part in the mixing of
-values with the first such layer's); ``general_delta``: ``heads``, ``dim`` (and, optionally, ``decay_rank``: the low
+values: the earliest layer that does is their source); ``general_delta``: ``heads``, ``dim`` (and, optionally, ``decay_rank``: the low
 rank of the decay's projection, which a weight file shows by its tensors' shapes); ``hgrn2``: ``heads``, ``dim``,
 ``vdim``.  Every size and constant comes from there; layers may differ from one another in all of them.
 """

@@ -12,7 +12,7 @@
 //
 // `bias_kv_store_kernel` writes a step's keys and values into their pages and mixes the values on the way:
 // v <- (1 - lambda) v + lambda v_src with v_src the values that an earlier layer computed for the same tokens
-// (that layer leaves them in a float32 buffer: mode "source"); what is cached is the mixed value.
+// (that layer leaves them in a float32 buffer: mode "source"); the pages receive the value after mixing.
 //
 // `bias_attn_kernel`: rows of a block are (token, head) pairs that share a key/value head, so a key tile
 // fetched once serves all of a group's heads; 32 rows x 32 keys a round, online softmax, float32 on the CUDA

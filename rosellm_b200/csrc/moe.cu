@@ -1,7 +1,8 @@
 // Mixture of experts: routing, and the experts' gated feed-forward as grouped products.
 //
 // Routing (`moe_select_kernel`, one warp per token, float32): scores s = softmax(z) over all
-// experts, or (score_kind 1) s = sigmoid(z) of each expert by itself; the choice is made on s + correction, the weights are the chosen experts' s.  With
+// experts, or (score_kind 1) s = sigmoid(z) of each expert by itself; the choice is made on s + correction,
+// the weights are the chosen experts' s.  With
 // groups, the experts form `group_count` equal groups of neighbours, a group's score is the
 // largest choice score in it, and only experts of the best `group_keep` groups can be chosen
 // (the others count as minus infinity).  Ties go to the lower index.

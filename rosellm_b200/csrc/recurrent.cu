@@ -4,9 +4,9 @@
 // Two forms share the kernels (MODE):
 //   0, the generalized delta rule: per key channel a decay w = exp(-decay_scale * sigmoid(w0 + W2 tanh(p)))
 //     (p: a low-rank projection of the layer's input), a removal rate a = sigmoid(a' + a_bias), the unit key
-//     u = k / sqrt(sum k^2 + unit_eps); the removal term and the decay both read the old state.  Output: each
+//     u = k / sqrt(sum k^2 + unit_eps); decay and removal both act on S_(t-1).  Output: each
 //     head's o divided by its root mean square, times a weight per (head, column), times sigmoid(g).
-//   1, a gated linear recurrence in which the forget gate also decides what is written: f = l + (1 - l) *
+//   1, a gated linear recurrence with one gate for forgetting and writing: f = l + (1 - l) *
 //     sigmoid(f' + f_bias), w = f, k = 1 - f, r = silu(q'), no removal.  Output: each head's o RMS-normed with
 //     a weight per column that the heads share.
 //

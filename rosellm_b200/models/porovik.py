@@ -3,7 +3,7 @@
 A decoder-only model whose layers differ in their mixers: causal attention with a distance bias and a
 query temperature (no rotation), a generalized delta rule, and a gated linear recurrence, in whatever
 order ``config.json`` lists them.  The embedding adds a hashed table of token pairs and a learned position
-table; every sublayer has an RMS norm ahead of it and one behind it, with scales stored around zero
+table; every sublayer has an RMS norm ahead of it and one behind it, with scales kept as offsets from one
 (``1 + w``); the feed-forward is dense (tanh-GELU gate) or a mixture of experts (sigmoid scores, the
 weight on the expert's input, SiLU gate); a final norm and the embedding table as the head.
 

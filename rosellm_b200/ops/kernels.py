@@ -1295,7 +1295,7 @@ def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_
     """The step's keys ``k`` [tokens, kv heads * dk] and values ``v`` [tokens, kv heads * dv] (float32 views)
     into the pool [pages, 1, kv heads, page, row], the value at entry ``v_at`` of a row.  ``mix`` 1: the
     values are also left in ``v_src`` (float32 [tokens, kv heads * dv]); 2: v <- (1 - lam) v + lam v_src
-    (``lam`` a float32 device scalar) is what is cached."""
+    (``lam`` a float32 device scalar) goes into the pages."""
     _need(k, "k", torch.float32, contiguous=False)
     _need(v, "v", torch.float32, contiguous=False)
     _need(pool, "pool")

@@ -27,7 +27,7 @@ class BiasedAttention(Part):
         score = (q . k) * scale * (1 + temp_coef * ln(floor((i + 1) / temp_every) + 1)) - slope_h * (i - j)
 
     with ``slope_h = 2^(-slope_log2_span * (h + 1) / num_heads)`` (``slope_log2_span = 0``: no bias;
-    ``temp_every = 0``: no temperature), an ordinary softmax over the visible keys, and the merged heads
+    ``temp_every = 0``: no temperature), a plain softmax over the keys a query may see, and the merged heads
     multiplied by ``sigmoid(W_g h)`` (``gate``) ahead of ``W_o``.
 
     ``value_mix``: ``"source"`` leaves the step's values for later layers; ``"mix"`` replaces its own by

@@ -69,7 +69,7 @@ class DeltaRuleMixer(_StateMixer):
     """The generalized delta rule.  ``r, k, v = W_r h, W_k h, W_v h`` (heads x dim each); per head and key
     channel a decay ``w = exp(-decay_scale * sigmoid(w0 + W_w2 tanh(W_w1 h)))`` and a removal rate
     ``a = sigmoid(W_a h + a_bias)``; with the unit key ``u = k / sqrt(sum k^2 + unit_eps)``:
-    ``S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T`` (both terms read the old state) and
+    ``S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T`` (decay and removal both act on ``S_(t-1)``) and
     ``o_t = S_t^T r``.  Each head's ``o`` is divided by its root mean square (``norm_eps``), multiplied by
     ``out_norm`` (one entry per head and column) and by ``sigmoid(W_g h)``, then ``W_o``.
     ``low_rank``: the inner size of the decay's projection; ``None`` takes it from the bound tensors."""
@@ -125,7 +125,7 @@ class DeltaRuleMixer(_StateMixer):
 
 @register_part("mixer", "gated_recurrence")
 class GatedRecurrenceMixer(_StateMixer):
-    """Linear attention in which the forget gate also decides what is written.  ``q = silu(W_q h)`` (heads x
+    """A linear recurrence with one gate for forgetting and writing: what a channel does not keep, it takes from the value.  ``q = silu(W_q h)`` (heads x
     key_dim), ``v = W_v h`` (heads x value_dim), ``f = l + (1 - l) * sigmoid(W_f h + f_bias)`` with the lower
     bound ``l`` per head and key channel; ``S_t = diag(f) S_(t-1) + (1 - f) v^T``, ``o_t = S_t^T q``.  Each
     head's ``o`` is RMS-normed over value_dim with a weight the heads share (``norm_eps``), then ``W_o``."""

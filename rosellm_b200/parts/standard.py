@@ -114,7 +114,7 @@ class TokenEmbedding(Part):
 class TokenPairEmbedding(Part):
     """``x = table[token] + pair_table[(previous token * mul_prev + token * mul_cur) mod buckets]`` (+ the
     position table's row): a second, hashed table indexed by the pair of neighbouring tokens; a
-    sequence's first token takes the table's last row, number ``buckets``.
+    sequence's first token has no pair and takes row ``buckets``, which the table holds beyond its buckets.
 
     The previous token of a portion's first token is the request's own state (one int32 in its
     state slot, kept up to date by the kernel), so a prompt may be cut anywhere."""
@@ -181,7 +181,7 @@ class LayerNorm(Part):
 @register_part("norm", "rms_norm")
 class RMSNorm(Part):
     """``x / sqrt(mean(x^2) + eps) * (weight_offset + weight)`` over the last dimension, in float32
-    (``weight_offset`` 1 for scales that are stored around zero; the sum is formed once, when the
+    (``weight_offset`` 1 for scales kept as offsets from one; the sum is formed once, when the
     weights are bound).
 
     ``forward`` normalises rows of the stream for a consumer (a head, a pre-norm block).

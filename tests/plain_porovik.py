@@ -18,7 +18,7 @@ def rms(x, eps):
 
 
 def norm(x, w, eps):
-    """Scales are stored around zero."""
+    """The file holds a scale as its offset from one."""
     return rms(x, eps) * (1.0 + w)
 
 

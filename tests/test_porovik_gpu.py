@@ -33,7 +33,7 @@ def dev(a):
 
 def test_pair_embedding_over_portions_and_reused_slots():
     """The previous token of a portion's first token comes from the slot's state; a sequence's first
-    token takes the last row; a slot that is taken again starts anew when its state was zeroed."""
+    token takes row ``buckets``; a slot that is taken again starts anew when its state was zeroed."""
     from rosellm_b200.engine.context import build_host_batch
 
     g = torch.Generator().manual_seed(1)
