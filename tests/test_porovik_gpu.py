@@ -433,6 +433,30 @@ def test_first_tokens_and_long_decoding(folders, tmp_path, dtype):
     check(folders["B", dtype], reqs, tr, replay(folders["B", dtype], "B", dtype, tr, tmp_path / "long", cuda_graphs=True), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wide_model_with_long_contexts(tmp_path, dtype):
+    """Width 1024: the products' tensor-core paths with float32 outputs, prompts of 600 and 350 tokens whole
+    and in portions of up to 256, the last tokens one by one over contexts whose keys are cut into parts,
+    states of 64 and 128 columns spread over several blocks."""
+    from tiny_porovik import WIDE
+
+    folder = write_tiny("WIDE", str(tmp_path), decisive=dtype == "bfloat16")
+    rng = np.random.default_rng(3)
+    reqs = {f"r{i}": rng.integers(0, WIDE["raw"]["vocab"], size=n).tolist() for i, n in enumerate([600, 350])}
+    for i, tr in enumerate((R.whole(reqs), R.tail_decoded(reqs, tail=6), R.portions(reqs, sizes=(256, 3, 130, 64, 200)))):
+        wanted = {rid: {len(t) - 1, len(t) - 2, len(t) // 2, 0, 1} for rid, t in reqs.items()}
+        for s_, w_ in zip(tr.steps, tr.wanted):  # keep a few rows a request: the logits of 950 rows are not needed
+            keep = [k for k, (rid, pos) in enumerate(w_) if pos in wanted[rid] or len(s_["entries"][0]["tokens"]) == 1]
+            at = 0
+            for e in s_["entries"]:
+                n = len(e["want"])
+                e["want"] = [e["want"][k - at] for k in keep if at <= k < at + n]
+                at += n
+            w_[:] = [w_[k] for k in keep]
+        got = R.replay(folder, dtype, tr, str(tmp_path / f"w{i}"), page_size=16)
+        check(folder, reqs, tr, got, dtype)
+
+
 def test_trace_program_as_a_child_process(folders, tmp_path):
     reqs = requests_for("A", [40, 90, 3], 6)
     tr = R.mixed(reqs, {rid: len(t) - 5 for rid, t in reqs.items()}, max_live=2, seed=1)

@@ -93,6 +93,16 @@ TINY = {
     "E": dict(raw=RAW_E, seed=25, std=0.3, page_size=16),
     "F": dict(raw=RAW_F, seed=26, std=0.3, page_size=8),
 }
+# A wide one, for the products' tensor-core paths, contexts of many key tiles and states of 64 and 128
+# columns: sixteen heads on four key/value heads of 64/64, a delta rule of 16 x 64 x 64, a gated
+# recurrence of 8 x 128 x 128, sixteen experts of 512.  Not among the models every test runs on.
+RAW_WIDE = model(3000, 1024, 1024, 1e-5, (65521, 36313, 27191), [
+    (attn(16, 4, 64, 64, 0.125, temp=(0.5, 128), v_mix=True), dense(2048)),
+    (delta(16, 64, 64), moe(512, 16, 2)),
+    (gated(8, 128, 128), dense(2048)),
+    (attn(16, 4, 64, 64, 0.125, temp=(0.5, 128), v_mix=True), moe(512, 16, 2)),
+])
+WIDE = dict(raw=RAW_WIDE, seed=31, std=0.03, page_size=16)
 
 
 def write_tiny(name: str, root: str, decisive: bool = False) -> str:
@@ -106,7 +116,7 @@ def write_tiny(name: str, root: str, decisive: bool = False) -> str:
     unlike experts are what the 32-bit runs test."""
     from safetensors.torch import load_file, save_file
 
-    t = TINY[name]
+    t = WIDE if name == "WIDE" else TINY[name]
     out = os.path.join(root, f"porovik_{name}" + ("_decisive" if decisive else ""))
     if not os.path.isfile(os.path.join(out, "model.safetensors")):
         write_model_folder(PorovikConfig.from_dict(t["raw"]), t["seed"], out, std=t["std"], norm_affine="random")
