@@ -50,6 +50,12 @@ struct BiasAttnParams {
   float* part_ml;
 };
 
+}  // namespace rl
+
+#include "bias_attention_mma.cuh"
+
+namespace rl {
+
 // LPR lanes share a row (their keys tx + LPR b, their value columns tx + LPR c), RPT rows a thread: a block has
 // (BA_THREADS / LPR) * RPT rows.  Prompt tiles run 8 lanes x 2 rows (32 rows); a decoded token has only its
 // group's heads as rows, so its blocks run 16 or 32 lanes a row (8 or 4 rows) and every thread has work.
@@ -389,13 +395,14 @@ static void dispatch_bias_attn_types(int cache_dtype, int out_dtype, const BiasA
 
 }  // namespace rl
 
-// How a block's 32 rows are cut into tokens and heads for `heads_per_group` query heads a key/value head:
-// heads a block (at most 32) and tokens a block (a power of two, at most 32).
-RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int* heads_per_block, int* tokens_per_block) {
-  if (heads_per_group <= 0) return -2;
-  const int hb = heads_per_group < rl::BA_ROWS ? heads_per_group : rl::BA_ROWS;
+// How the `rows` rows of a prompt tile's block (32: the CUDA-core kernel; 64: the tensor-core kernel) are cut
+// into tokens and heads for `heads_per_group` query heads a key/value head: heads a block (at most `rows`) and
+// tokens a block (a power of two, at most `rows`).
+RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int rows, int* heads_per_block, int* tokens_per_block) {
+  if (heads_per_group <= 0 || (rows != rl::BA_ROWS && rows != rl::BM_ROWS)) return -2;
+  const int hb = heads_per_group < rows ? heads_per_group : rows;
   int tt = 1;
-  while (tt * 2 * hb <= rl::BA_ROWS) tt *= 2;
+  while (tt * 2 * hb <= rows) tt *= 2;
   *heads_per_block = hb;
   *tokens_per_block = tt;
   return 0;
@@ -403,6 +410,8 @@ RL_EXPORT int rl_bias_attention_shape(int heads_per_group, int* heads_per_block,
 
 // n_splits > 1: every decoded request's keys are cut into so many parts, a block each, merged by a second
 // kernel; part_o float32 [n_decode * heads * n_splits, dv], part_ml float32 [n_decode * heads * n_splits, 2].
+// tensor_cores: prompt tiles go to `bias_attn_mma_kernel` where the types and sizes allow (64 rows a block: the
+// tiles must then be cut as rl_bias_attention_shape(.., 64, ..) says).
 // tiles: (request, first new token) of portions cut every `tile_tokens` tokens (a multiple of the tokens a
 // block takes); decode_reqs: the requests that bring one token.  cache_dtype: the pool's element type;
 // out_dtype: that of out.
@@ -412,13 +421,15 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
                                 const int* decode_reqs, int n_decode, void* out, long ldo, int n_heads, int n_kv, int dk,
                                 int dv, int v_at, int row, int page_size, int max_pages, float scale, float temp_coef,
                                 int temp_every, const float* slopes, int* status, int n_splits, float* part_o,
-                                float* part_ml, cudaStream_t stream) {
+                                float* part_ml, int tensor_cores, cudaStream_t stream) {
   if (n_tiles <= 0 && n_decode <= 0) return 0;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || dk <= 0 || dk > 256 || dv <= 0 || dv > 256 || v_at < dk ||
       v_at + dv > row || n_kv > 65535)
     return -2;
+  // prompt tiles on the tensor cores: bfloat16 cache and output, per-head sizes up to 128
+  const bool mma = tensor_cores && cache_dtype == RL_BF16 && out_dtype == RL_BF16 && dk <= 128 && dv <= 128;
   int hb, tt;
-  rl_bias_attention_shape(n_heads / n_kv, &hb, &tt);
+  rl_bias_attention_shape(n_heads / n_kv, mma ? rl::BM_ROWS : rl::BA_ROWS, &hb, &tt);
   if (n_tiles > 0 && (tile_tokens < tt || tile_tokens % tt)) return -3;
   if (n_tiles <= 0) tile_tokens = tt;
   if (n_splits < 1 || n_splits > 32 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr))) return -4;
@@ -427,9 +438,11 @@ RL_EXPORT int rl_bias_attention(int cache_dtype, int out_dtype, const float* q, 
   rl::BiasAttnParams p{q, ldq, gate, ldg, pool, block_table, ldt, q_start, kv_len, slots, tiles, decode_reqs, out, ldo,
                        n_heads, n_kv, dk, dv, v_at, row, page_size, max_pages, n_tiles > 0 ? n_tiles : 0, tile_tokens,
                        tt, hb, 0, scale, temp_coef, temp_every, slopes, status, 1, part_o, part_ml};
-  if (p.n_tiles > 0)  // the prompt portions: 32 rows a block, cut into tokens and heads as rl_bias_attention_shape says
-    rl::dispatch_bias_attn_types(cache_dtype, out_dtype, p, 32, dim3(p.n_tiles * (tile_tokens / tt), n_kv, (hg + hb - 1) / hb),
-                                 stream);
+  if (p.n_tiles > 0) {  // the prompt portions: 32 or 64 rows a block, cut into tokens and heads as rl_bias_attention_shape says
+    const dim3 grid(p.n_tiles * (tile_tokens / tt), n_kv, (hg + hb - 1) / hb);
+    if (mma) rl::dispatch_bias_attn_mma(p, grid, stream);
+    else rl::dispatch_bias_attn_types(cache_dtype, out_dtype, p, 32, grid, stream);
+  }
   if (n_decode > 0) {  // the decoded tokens: a block's rows are heads of one group, 4, 8 or 32 of them
     const int rows = hg <= 4 ? 4 : (hg <= 8 ? 8 : 32);
     p.n_tiles = 0;

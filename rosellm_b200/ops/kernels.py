@@ -171,9 +171,9 @@ def _lib() -> ctypes.CDLL:
         lib.rl_rmsnorm_add_norm.argtypes = [I, P, L, P, P, L, P, P, L, I, I, F, F, P]
         lib.rl_recurrence.argtypes = [I, I, P, L, I, I, I, I, I, I, P, P, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, F, F, F, P]
         lib.rl_recurrence_record.argtypes = [I, I, I, P, P, P]
-        lib.rl_bias_attention_shape.argtypes = [I, P, P]
+        lib.rl_bias_attention_shape.argtypes = [I, I, P, P]
         lib.rl_bias_attention.argtypes = [I, I, P, L, P, L, P, P, L, P, P, P, P, I, I, P, I, P, L, I, I, I, I, I, I, I, I,
-                                          F, F, I, P, P, I, P, P, P]
+                                          F, F, I, P, P, I, P, P, I, P]
         lib.rl_bias_kv_store.argtypes = [I, P, L, P, L, P, P, I, P, P, L, P, P, P, I, I, I, I, I, I, I, I, P, P]
         for name in ("rl_rmsnorm", "rl_rmsnorm_add", "rl_cast_rows", "rl_latent_attention_fits", "rl_latent_decode_fits",
                      "rl_latent_kv_write", "rl_latent_q_rope", "rl_latent_attention", "rl_head_linear", "rl_gated_act",
@@ -1282,10 +1282,19 @@ def recurrence(mode: int, proj, offsets: dict, state, out, q_start, slots, prep,
 
 # ---- attention with a distance bias over rows of [key | value] -------------------------------------
 
-def bias_attention_shape(heads_per_group: int) -> tuple[int, int]:
-    """(heads a block, tokens a block) of ``bias_attention`` for so many query heads a key/value head."""
+BIAS_ATTENTION_TENSOR_CORES = True  # prompt portions in bfloat16 on mma.sync (off: the CUDA-core kernel throughout)
+
+
+def bias_attention_tensor_cores(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """Whether ``bias_attention`` may be asked for its tensor-core form for prompt portions."""
+    return BIAS_ATTENTION_TENSOR_CORES and dtype == torch.bfloat16 and dk <= 128 and dv <= 128
+
+
+def bias_attention_shape(heads_per_group: int, tensor_cores: bool = False) -> tuple[int, int]:
+    """(heads a block, tokens a block) of ``bias_attention``'s prompt tiles for so many query heads a
+    key/value head: of the 32 rows of the CUDA-core kernel's blocks, or the 64 of the tensor-core kernel's."""
     hb, tt = c_int(0), c_int(0)
-    if _lib().rl_bias_attention_shape(int(heads_per_group), ctypes.byref(hb), ctypes.byref(tt)) != 0:
+    if _lib().rl_bias_attention_shape(int(heads_per_group), 64 if tensor_cores else 32, ctypes.byref(hb), ctypes.byref(tt)) != 0:
         raise KernelError("bias_attention_shape: heads per group must be positive")
     return hb.value, tt.value
 
@@ -1323,8 +1332,10 @@ def bias_kv_store(k, v, pool, block_table, positions, req_of_token, slots, *, v_
 def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n_heads: int, dk: int, dv: int, v_at: int,
                    scale: float, slopes=None, temp_coef: float = 0.0, temp_every: int = 0, tiles=None, n_tiles: int = 0,
                    tile_tokens: int = 16, decode_reqs=None, n_decode: int = 0, max_pos: int, n_splits: int = 1, part_o=None,
-                   part_ml=None) -> None:
+                   part_ml=None, tensor_cores: bool = False) -> None:
     """Causal attention of the step's queries over the cached rows (csrc/bias_attention.cu).
+    ``tensor_cores``: prompt portions on mma.sync (bfloat16 pool and output, sizes up to 128; the tiles cut as
+    ``bias_attention_shape(.., True)`` says).
     ``n_splits`` > 1: the keys of every decoded request are cut into so many parts (``part_o`` float32
     [n_decode * heads * n_splits, dv] and ``part_ml`` [.., 2] are their scratch) and merged in order.
     ``q`` float32 [tokens, heads * dk] and ``gate`` float32 [tokens, heads * dv] (or ``None``) may be views
@@ -1357,7 +1368,8 @@ def bias_attention(q, gate, pool, block_table, q_start, kv_len, slots, out, *, n
                                   _ptr(out), out.stride(0), n_heads, n_kv, dk, dv, int(v_at), row, page_size,
                                   min(block_table.shape[1], -(-max_pos // page_size)), float(scale), float(temp_coef),
                                   int(temp_every), _ptr(slopes), _ptr(status_word(out.device)), int(n_splits), _ptr(part_o),
-                                  _ptr(part_ml), _stream())
+                                  _ptr(part_ml), int(bool(tensor_cores) and bias_attention_tensor_cores(pool.dtype, dk, dv)
+                                                     and out.dtype == torch.bfloat16), _stream())
     if rc in (-2, -3, -4):
         raise KernelError(f"bias_attention: sizes not taken (code {rc}: key and value sizes up to 256; tiles a multiple "
                           "of the tokens a block takes)")

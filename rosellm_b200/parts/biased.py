@@ -36,7 +36,8 @@ class BiasedAttention(Part):
 
     The cache keeps one row a token and key/value head: the key's ``key_dim`` entries, then (from a
     multiple of 8 on) the value's ``value_dim``.  All four projections are one product writing float32;
-    scores, softmax and the weighted sums are float32 in both precisions."""
+    scores, softmax and the weighted sums are float32 in both precisions (in bfloat16 mode the prompt
+    portions' two products take bfloat16 operands on the tensor cores and accumulate in float32)."""
 
     graph_safe = True
     launches_replayable = True
@@ -132,8 +133,9 @@ class BiasedAttention(Part):
         else:  # the fill stays zero: see the state mixers' output buffer
             buf = ws.get_zeroed(f"biased_attn_out_{self.out_width}_{self.out_padded}", (n, self.out_padded), ctx.act_dtype)
             out = buf[:, :self.out_width]
-        if self._shape is None:
-            self._shape = K.bias_attention_shape(self.num_heads // self.num_kv_heads)
+        mma = K.bias_attention_tensor_cores(ctx.act_dtype, self.key_dim, self.value_dim)
+        if self._shape is None or self._shape[0] != mma:
+            self._shape = (mma, K.bias_attention_shape(self.num_heads // self.num_kv_heads, mma)[1])
         wide = self._shape[1] > 16  # the tokens a block takes must divide the tiles the step is cut into
         splits = (ctx.extras.get("decode_plan") or self.decode_plan_for(ctx.n_decode, ctx.max_kv_len))[0]
         part_o = part_ml = None
@@ -146,5 +148,5 @@ class BiasedAttention(Part):
                          temp_coef=self.temp_coef, temp_every=self.temp_every,
                          tiles=ctx.tiles_wide if wide else ctx.tiles, n_tiles=ctx.n_tiles_wide if wide else ctx.n_tiles,
                          tile_tokens=64 if wide else 16, decode_reqs=ctx.decode_reqs, n_decode=ctx.n_decode,
-                         max_pos=ctx.cache.max_seq_len, n_splits=splits, part_o=part_o, part_ml=part_ml)
+                         max_pos=ctx.cache.max_seq_len, n_splits=splits, part_o=part_o, part_ml=part_ml, tensor_cores=mma)
         K.linear(buf, self.out_weight, None, x, residual=add)

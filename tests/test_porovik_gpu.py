@@ -79,7 +79,8 @@ def test_norm_with_scales_around_zero_and_the_fused_pair(width):
         assert rel(nxt.float(), P.norm(want_x, w2.double(), 1e-3)) < tol
 
 
-def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, seed, stand_out=None, gate=True, splits=1):
+def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, seed, stand_out=None, gate=True, splits=1,
+                    mma=False):
     """Requests with ``lens_old`` cached tokens bring ``lens_new`` more.  The cache rows of all tokens are
     written by the store kernel (old tokens in a step of their own); returns the kernel's output
     [tokens, H, dv] and the plain result from the same (rounded) keys and values."""
@@ -122,7 +123,8 @@ def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, 
                           v_at=v_at, max_pos=max(totals))
     slopes = distance_slopes(H, 8.0)
     gate_t = torch.randn(n_tok, H * dv, generator=g) if gate else None
-    wide = K().bias_attention_shape(H // G)[1] > 16
+    mma = mma and K().bias_attention_tensor_cores(dt, dk, dv)
+    wide = K().bias_attention_shape(H // G, mma)[1] > 16
     tiles, n_tiles = (hb.tiles_wide, len(hb.tiles_wide)) if wide else (hb.tiles, len(hb.tiles))
     out = torch.full((n_tok, H * dv), 5.0, dtype=dt, device=DEV)
     part_o = part_ml = None
@@ -133,7 +135,8 @@ def _attention_case(dtype, H, G, dk, dv, lens_new, lens_old, page, scale, temp, 
                        dev(hb.q_start), dev(hb.kv_len), dev(hb.slots), out, n_heads=H, dk=dk, dv=dv, v_at=v_at, scale=scale,
                        slopes=slopes.to(DEV), temp_coef=temp[0], temp_every=temp[1], tiles=dev(tiles.reshape(-1)),
                        n_tiles=n_tiles, tile_tokens=64 if wide else 16, decode_reqs=dev(hb.decode_reqs),
-                       n_decode=len(hb.decode_reqs), max_pos=max(totals), n_splits=splits, part_o=part_o, part_ml=part_ml)
+                       n_decode=len(hb.decode_reqs), max_pos=max(totals), n_splits=splits, part_o=part_o, part_ml=part_ml,
+                       tensor_cores=mma)
     K().check_status(torch.device(DEV))
     want = torch.empty(n_tok, H, dv, dtype=torch.float64)
     t0 = 0
@@ -155,15 +158,20 @@ def test_biased_attention_prompt_portions_and_single_tokens(dtype):
     """Portions that start inside a page and end on a page's border, of one to 40 tokens, beside single
     tokens; groups of three and of forty heads a key/value head, as many key/value heads as heads; a
     query temperature that steps inside the portions."""
-    tol = 2e-5 if dtype == "float32" else 1e-2
-    for H, G, dk, dv, page, temp in ((6, 2, 20, 10, 16, (0.7, 16)), (4, 4, 64, 32, 8, (0.0, 0)), (40, 1, 8, 8, 32, (0.1, 1)),
-                                     (5, 1, 16, 72, 8, (1.5, 33)), (2, 1, 130, 136, 16, (0.3, 7))):
-        got, want = _attention_case(dtype, H, G, dk, dv, [40, 1, 2, 17, 1, 16], [5, 130, 0, 15, 0, 16], page, 0.3, temp, seed=H)
-        assert rel(got, want) < tol, (H, G, dk, dv)
-        got, want = _attention_case(dtype, H, G, dk, dv, [33, 16, 2, 70], [0, 31, 70, 63], page, 0.2, temp, seed=H + 9, gate=False)
-        assert rel(got, want) < tol, (H, G, dk, dv, "portions only")
-        got, want = _attention_case(dtype, H, G, dk, dv, [1, 1, 1], [0, 31, 32], page, 0.2, temp, seed=H + 50)
-        assert rel(got, want) < tol, (H, G, dk, dv, "single tokens")
+    for mma in ((False,) if dtype == "float32" else (False, True)):
+        # with bfloat16 operands on the tensor cores the queries and the probabilities are rounded too
+        tol = 2e-5 if dtype == "float32" else (2.5e-2 if mma else 1e-2)
+        for H, G, dk, dv, page, temp in ((6, 2, 20, 10, 16, (0.7, 16)), (4, 4, 64, 32, 8, (0.0, 0)), (40, 1, 8, 8, 32, (0.1, 1)),
+                                         (5, 1, 16, 72, 8, (1.5, 33)), (2, 1, 130, 136, 16, (0.3, 7)), (16, 4, 128, 128, 16, (0.5, 50)),
+                                         (80, 1, 24, 40, 16, (0.2, 9))):
+            got, want = _attention_case(dtype, H, G, dk, dv, [40, 1, 2, 17, 1, 16], [5, 130, 0, 15, 0, 16], page, 0.3, temp, seed=H,
+                                        mma=mma)
+            assert rel(got, want) < tol, (H, G, dk, dv, mma)
+            got, want = _attention_case(dtype, H, G, dk, dv, [33, 16, 2, 70], [0, 31, 70, 63], page, 0.2, temp, seed=H + 9, gate=False,
+                                        mma=mma)
+            assert rel(got, want) < tol, (H, G, dk, dv, mma, "portions only")
+            got, want = _attention_case(dtype, H, G, dk, dv, [1, 1, 1], [0, 31, 32], page, 0.2, temp, seed=H + 50, mma=mma)
+            assert rel(got, want) < tol, (H, G, dk, dv, mma, "single tokens")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -183,10 +191,10 @@ def test_a_far_key_that_stands_out_is_found(dtype, key):
     """Among 900 cached keys one is scored far above the rest for the head with the smallest slope: the
     output must be (nearly) that key's value, whether it is the first, sits at a page's border or far
     back; from a prompt portion's query and from a decoded token's."""
-    for new, old, splits in (([4], [896], 1), ([1], [899], 1), ([1], [899], 5)):
+    for new, old, splits, mma in (([4], [896], 1, False), ([4], [896], 1, True), ([1], [899], 1, False), ([1], [899], 5, False)):
         got, want = _attention_case(dtype, 4, 2, 24, 12, new, old, 16, 0.5, (0.0, 0), seed=key, stand_out=(key, 3), gate=False,
-                                    splits=splits)
-        assert rel(got, want) < (2e-5 if dtype == "float32" else 1e-2)
+                                    splits=splits, mma=mma)
+        assert rel(got, want) < (2e-5 if dtype == "float32" else 2.5e-2)
 
 
 def test_distance_bias_and_temperature_enter_the_scores():
