@@ -180,8 +180,45 @@ __global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const Recur
   };
   fetch(0);
   constexpr bool AHEAD = NV * DKQ <= 80;  // two sets of a token's vectors fit the registers
-  TokenVectors<MODE, NV, DKQ> cur;
-  TokenVectors<MODE, NV, AHEAD ? DKQ : 4> nxt;
+  float* Po = seq_s + (size_t)2 * chunk * rec;  // [chunk][threads]: every thread's share of S^T r, summed after the chunk
+  // One token: the state's update, and this thread's share of the output, parked in shared memory (its sum
+  // over the lanes of a column is not on the way to the next token, so it waits for the end of the chunk).
+  auto step = [&](const auto& tv, int t) {
+    const float vj = tv.value;
+    float pj = 0.f;
+    if (MODE == 0) {
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int m = 0; m < DKQ / 4; ++m) {
+        const float4 u = tv.v[3][m];
+        a0 = fmaf(u.x, S[4 * m], fmaf(u.y, S[4 * m + 1], a0));
+        a1 = fmaf(u.z, S[4 * m + 2], fmaf(u.w, S[4 * m + 3], a1));
+      }
+      pj = a0 + a1;
+#pragma unroll
+      for (int o = 1; o < TPC; o <<= 1) pj += __shfl_xor_sync(0xffffffffu, pj, o);
+    }
+    float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+    for (int m = 0; m < DKQ / 4; ++m) {
+      const float4 w = tv.v[0][m], k = tv.v[1][m], r = tv.v[2][m];
+      float4 au = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (MODE == 0) au = tv.v[NV - 1][m];
+      const float s0 = fmaf(w.x, S[4 * m], fmaf(-au.x, pj, k.x * vj));
+      const float s1 = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, pj, k.y * vj));
+      const float s2 = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, pj, k.z * vj));
+      const float s3 = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, pj, k.w * vj));
+      S[4 * m] = s0;
+      S[4 * m + 1] = s1;
+      S[4 * m + 2] = s2;
+      S[4 * m + 3] = s3;
+      o0 = fmaf(s0, r.x, fmaf(s1, r.y, o0));
+      o1 = fmaf(s2, r.z, fmaf(s3, r.w, o1));
+    }
+    Po[t * blockDim.x + threadIdx.x] = o0 + o1;
+  };
+  TokenVectors<MODE, NV, DKQ> va;
+  TokenVectors<MODE, NV, AHEAD ? DKQ : 4> vb;
   for (int c = 0; c < n_chunks; ++c) {
     if (c + 1 < n_chunks) {
       fetch(c + 1);
@@ -192,53 +229,35 @@ __global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const Recur
     __syncthreads();
     const int nt = min(chunk, n_tok - c * chunk);
     const float* buf = seq_s + (size_t)(c & 1) * chunk * rec;
-    take(buf, cur);
-    for (int t = 0; t < nt; ++t) {
-      if constexpr (AHEAD) {
-        if (t + 1 < nt) take(buf + (size_t)(t + 1) * rec, nxt);
-      }
-      const float vj = cur.value;
-      float pj = 0.f;
-      if (MODE == 0) {
-        float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-        for (int m = 0; m < DKQ / 4; ++m) {
-          const float4 u = cur.v[3][m];
-          a0 = fmaf(u.x, S[4 * m], fmaf(u.y, S[4 * m + 1], a0));
-          a1 = fmaf(u.z, S[4 * m + 2], fmaf(u.w, S[4 * m + 3], a1));
+    if constexpr (AHEAD) {  // two sets of registers in turn: a token's vectors are on their way while the one before is worked on
+      take(buf, va);
+      for (int t = 0; t < nt; t += 2) {
+        if (t + 1 < nt) take(buf + (size_t)(t + 1) * rec, vb);
+        step(va, t);
+        if (t + 1 < nt) {
+          if (t + 2 < nt) take(buf + (size_t)(t + 2) * rec, va);
+          step(vb, t + 1);
         }
-        pj = a0 + a1;
-#pragma unroll
-        for (int o = 1; o < TPC; o <<= 1) pj += __shfl_xor_sync(0xffffffffu, pj, o);
       }
-      float o0 = 0.f, o1 = 0.f;
-#pragma unroll
-      for (int m = 0; m < DKQ / 4; ++m) {
-        const float4 w = cur.v[0][m], k = cur.v[1][m], r = cur.v[2][m];
-        float4 au = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (MODE == 0) au = cur.v[NV - 1][m];
-        const float s0 = fmaf(w.x, S[4 * m], fmaf(-au.x, pj, k.x * vj));
-        const float s1 = fmaf(w.y, S[4 * m + 1], fmaf(-au.y, pj, k.y * vj));
-        const float s2 = fmaf(w.z, S[4 * m + 2], fmaf(-au.z, pj, k.z * vj));
-        const float s3 = fmaf(w.w, S[4 * m + 3], fmaf(-au.w, pj, k.w * vj));
-        S[4 * m] = s0;
-        S[4 * m + 1] = s1;
-        S[4 * m + 2] = s2;
-        S[4 * m + 3] = s3;
-        o0 = fmaf(s0, r.x, fmaf(s1, r.y, o0));
-        o1 = fmaf(s2, r.z, fmaf(s3, r.w, o1));
-      }
-      float o = o0 + o1;
-#pragma unroll
-      for (int x = 1; x < TPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-      if (part == 0 && col < dv) p.oraw[(size_t)(t0 + c * chunk + t) * p.n_heads * dv + (size_t)head * dv + col] = o;
-      if constexpr (AHEAD) {
-        cur = nxt;
-      } else {
-        if (t + 1 < nt) take(buf + (size_t)(t + 1) * rec, cur);
+    } else {
+      for (int t = 0; t < nt; ++t) {
+        take(buf + (size_t)t * rec, va);
+        step(va, t);
       }
     }
-    __syncthreads();  // the buffer is free for the chunk after the next
+    __syncwarp();  // a column's lanes are lanes of one warp
+    // the chunk's outputs: (token, column) pairs over the block's threads, the column's parts summed in order
+    const int cols_here = blockDim.x / TPC;
+    for (int i = threadIdx.x; i < nt * cols_here; i += blockDim.x) {
+      const int t = i / cols_here, cl = i - t * cols_here;
+      const float* pp = Po + t * blockDim.x + cl * TPC;
+      float o = 0.f;
+#pragma unroll
+      for (int x = 0; x < TPC; ++x) o += pp[x];
+      const int cg = blockIdx.z * cols + cl;
+      if (cg < dv) p.oraw[(size_t)(t0 + c * chunk + t) * p.n_heads * dv + (size_t)head * dv + cg] = o;
+    }
+    __syncthreads();  // the buffer is free for the chunk after the next, the parked shares have been read
   }
 #pragma unroll
   for (int k = 0; k < DKQ; ++k) {
@@ -273,18 +292,6 @@ __global__ __launch_bounds__(256) void recurrence_out_kernel(const RecurParams p
 
 template <int MODE, int TPC, int DKQ>
 static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
-  // tokens a buffer: as many as two buffers of about 48 KB hold, at most 16
-  int chunk = (int)(48 * 1024 / ((size_t)p.rec * sizeof(float)));
-  chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
-  const size_t smem = (size_t)2 * chunk * p.rec * sizeof(float);
-  auto kernel = recurrence_seq_kernel<MODE, TPC, DKQ>;
-  if (smem > 48 * 1024) {
-    static bool raised = false;
-    if (!raised) {
-      note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-      raised = true;
-    }
-  }
   // Columns a block: a token's work is a chain of dependent steps that every warp walks for itself, so few
   // columns a block and many blocks are what is fast, as long as there are SMs for them: halved from the
   // most a block takes until the grid fills the device (down to one warp).
@@ -301,6 +308,23 @@ static void launch_seq(const RecurParams& p, int n_reqs, cudaStream_t stream) {
   while (cols > per_warp && (long)n_reqs * p.n_heads * ((p.dv + cols - 1) / cols) < sms) cols /= 2;
   cols = (cols + per_warp - 1) / per_warp * per_warp;
   const int col_blocks = (p.dv + cols - 1) / cols;
+  // Tokens a buffer: a block's shared memory (two buffers of records and the parked output shares) is kept
+  // near 36 KB, so that three blocks fit an SM under the library's common split and a grid of up to three
+  // blocks an SM runs in one round (with 80 KB a block, the 256 blocks of a prompt step of two requests took
+  // two rounds: 515 us against 315);
+  // at most 16, at least 2.
+  const size_t per_token = ((size_t)2 * p.rec + (size_t)TPC * cols) * sizeof(float);
+  int chunk = (int)(36 * 1024 / per_token);
+  chunk = chunk < 2 ? 2 : (chunk > 16 ? 16 : chunk);
+  const size_t smem = (size_t)chunk * per_token;
+  auto kernel = recurrence_seq_kernel<MODE, TPC, DKQ>;
+  if (smem > 48 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      note_launch(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      raised = true;
+    }
+  }
   launch_pdl(kernel, dim3(n_reqs, p.n_heads, col_blocks), TPC * cols, smem, stream, p, chunk, cols);
 }
 
