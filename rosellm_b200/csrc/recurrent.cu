@@ -245,7 +245,7 @@ __global__ __launch_bounds__(REC_THREADS) void recurrence_seq_kernel(const Recur
         step(va, t);
       }
     }
-    __syncwarp();  // a column's lanes are lanes of one warp
+    __syncthreads();  // the shares of a column are summed by whichever thread the (token, column) pair falls to
     // the chunk's outputs: (token, column) pairs over the block's threads, the column's parts summed in order
     const int cols_here = blockDim.x / TPC;
     for (int i = threadIdx.x; i < nt * cols_here; i += blockDim.x) {

@@ -222,9 +222,13 @@ class Model:
         logits are made: ``None`` then too."""
         ctx.position = self.position
         x = self.embedding.forward(ctx, self.position)
-        for run in self.spec.run_order:
+        order = self.spec.run_order
+        for i, run in enumerate(order):
             layer = self.layers[run.layer]
+            # a block may finish with work of the layer that runs next (its first norm, say): it finds that layer here
+            ctx.extras["next_layer"] = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             layer.block.forward(ctx, run, layer, x)
+        ctx.extras.pop("next_layer", None)
         if ctx.n_logit_rows == 0:
             return None
         rows = ctx.host.logit_rows

@@ -575,8 +575,9 @@ class NormedSublayersBlock(Part):
 @register_part("block", "pre_post_norm")
 class PrePostNormBlock(Part):
     """Norms on both sides of every sublayer: ``x += norm_out(mixer(norm(x)))``, then (where the layer has
-    a feed-forward) ``x += norm_out(feed_forward(norm(x)))``, four norms of their own.  The norm behind
-    the mixer and the norm ahead of the feed-forward are one kernel."""
+    a feed-forward) ``x += norm_out(feed_forward(norm(x)))``, four norms of their own.  A norm behind a
+    sublayer and the norm ahead of the next one (the feed-forward's, or the first norm of the layer that
+    runs next) are one kernel: a layer launches two norm kernels, the model's first layer three."""
 
     graph_safe = True
     launches_replayable = True
@@ -588,20 +589,29 @@ class PrePostNormBlock(Part):
             self.uses.update(norm_feed_forward="norm", feed_forward="feed_forward", norm_feed_forward_out="norm")
 
     def forward(self, ctx, run, layer, x) -> None:
-        h = layer.norm_mixer.forward(ctx, x)
+        h = ctx.extras.pop("normed_ahead", None)  # left by the layer before, with its last addition to the stream
+        if h is None:
+            h = layer.norm_mixer.forward(ctx, x)
         y = ctx.workspace.get("sublayer_out", tuple(x.shape), torch.float32)
         layer.mixer.forward(ctx, run, h, y, add=False)
-        if not self.has_feed_forward:
-            layer.norm_mixer_out.add_to(ctx, y, x, 1.0)
-            return
-        fused = getattr(layer.norm_mixer_out, "add_then_norm", None)
-        if fused is not None and isinstance(layer.norm_feed_forward, RMSNorm):
-            h = fused(ctx, y, x, layer.norm_feed_forward)
+        last = layer.norm_mixer_out
+        if self.has_feed_forward:
+            fused = getattr(last, "add_then_norm", None)
+            if fused is not None and isinstance(layer.norm_feed_forward, RMSNorm):
+                h = fused(ctx, y, x, layer.norm_feed_forward)
+            else:
+                last.add_to(ctx, y, x, 1.0)
+                h = layer.norm_feed_forward.forward(ctx, x)
+            layer.feed_forward.forward(ctx, h, y, add=False)
+            last = layer.norm_feed_forward_out
+        # the layer's last addition to the stream, in one kernel with the first norm of the layer that runs next
+        # where that layer is arranged the same way
+        nxt = ctx.extras.get("next_layer")
+        follow = getattr(nxt, "norm_mixer", None) if nxt is not None and isinstance(nxt.block, PrePostNormBlock) else None
+        if isinstance(follow, RMSNorm) and hasattr(last, "add_then_norm"):
+            ctx.extras["normed_ahead"] = last.add_then_norm(ctx, y, x, follow)
         else:
-            layer.norm_mixer_out.add_to(ctx, y, x, 1.0)
-            h = layer.norm_feed_forward.forward(ctx, x)
-        layer.feed_forward.forward(ctx, h, y, add=False)
-        layer.norm_feed_forward_out.add_to(ctx, y, x, 1.0)
+            last.add_to(ctx, y, x, 1.0)
 
 
 @register_part("head", "tied_to_embedding")
