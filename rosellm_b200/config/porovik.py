@@ -149,8 +149,9 @@ class PorovikConfig(ModelConfig):
         if max(self.bigram_mul_prev, self.bigram_mul_cur, self.bigram_buckets) >= 2 ** 31:
             raise ConfigError("config.json: embedding.bigram: buckets and multipliers must fit 32-bit integers")
         mixing = [l.mixer for l in self.layers if l.type == "attention" and l.mixer.v_mix]
-        if any((m.kv_heads, m.vdim) != (mixing[0].kv_heads, mixing[0].vdim) for m in mixing):
-            raise ConfigError("config.json: layers that mix values (v_mix) must agree in kv_heads and vdim")
+        if any(m.kv_heads * m.vdim != mixing[0].kv_heads * mixing[0].vdim for m in mixing):
+            raise ConfigError("config.json: layers that mix values (v_mix) must have as many value entries a token "
+                              "(kv_heads * vdim) as the first of them")
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any]) -> "PorovikConfig":

@@ -73,7 +73,7 @@ def attention_mixer(h, W, p, mx, v_first):
             v_first = v
         else:
             lam = W[p + "vmix"]
-            v = (1.0 - lam) * v + lam * v_first
+            v = (1.0 - lam) * v + lam * v_first.reshape(v.shape)  # entry by entry of a token's values
     qt = mx.get("q_temp") or {}
     o = attention(q, k, v, mx["scale"], distance_slopes(H), query_temperature(n, qt.get("coef", 0.0), qt.get("every", 0)))
     o = o.reshape(n, H * dv) * torch.sigmoid(h @ W[p + "g"].T)

@@ -42,7 +42,7 @@ def test_refusals():
     raw = TINY["A"]["raw"]
     for path, value in ((("layers", 0, "type"), "conv"), (("layers", 0, "mixer", "kv_heads"), 4), (("width",), 60),
                         (("embedding", "bigram", "buckets"), 0), (("layers", 1, "mlp", "router", "top"), 9),
-                        (("layers", 3, "mixer", "vdim"), 12), (("norm", "eps"), 0.0), (("layers", 0, "mixer", "q_temp", "every"), 0)):
+                        (("layers", 3, "mixer", "vdim"), 12), (("layers", 3, "mixer", "kv_heads"), 1), (("norm", "eps"), 0.0), (("layers", 0, "mixer", "q_temp", "every"), 0)):
         bad = copy.deepcopy(raw)
         at = bad
         for k in path[:-1]:

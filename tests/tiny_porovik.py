@@ -83,7 +83,8 @@ RAW_E = model(90, 40, 600, 1e-5, (64, 5, 9), [
 ])
 RAW_F = model(64, 56, 600, 1e-5, (61, 1, 0), [
     (attn(7, 7, 9, 5, 0.33, temp=(2.0, 3)), None),
-    (attn(8, 1, 6, 11, 0.4, v_mix=True), dense(40)),
+    (attn(8, 1, 6, 12, 0.4, v_mix=True), dense(40)),
+    (attn(4, 2, 10, 6, 0.3, v_mix=True), None),   # as many value entries a token, cut into other heads
 ])
 TINY = {
     "A": dict(raw=RAW_A, seed=21, std=0.2, page_size=16),
@@ -91,7 +92,7 @@ TINY = {
     "C": dict(raw=RAW_C, seed=23, std=0.25, page_size=32),
     "D": dict(raw=RAW_D, seed=24, std=0.07, page_size=16),
     "E": dict(raw=RAW_E, seed=25, std=0.3, page_size=16),
-    "F": dict(raw=RAW_F, seed=26, std=0.3, page_size=8),
+    "F": dict(raw=RAW_F, seed=26, std=0.2, page_size=8),
 }
 # A wide one, for the products' tensor-core paths, contexts of many key tiles and states of 64 and 128
 # columns: sixteen heads on four key/value heads of 64/64, a delta rule of 16 x 64 x 64, a gated
